@@ -1,0 +1,116 @@
+/* libgdn_b200 -- C ABI of the B200 (sm_100a) GatedDeltaNet / GQA-decode kernels.
+ *
+ * The reference project (a Python/MLX code base) has no FFI layer: its operators are Python functions that JIT-compile
+ * Metal source.  Each entry point below is what a binding for one of those operators calls; the comment on each names
+ * the reference function it stands in for (paths relative to the reference project root).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the name ends in `_host`; bf16 tensors are passed as `void*`
+ *   - every function only enqueues work on `stream` (a cudaStream_t passed as void*; NULL = default stream); nothing
+ *     synchronises, allocates or retains caller memory
+ *   - the return value is 0 on success or one of the negative GDN_E_* codes; `gdn_last_error_string()` describes the last
+ *     failure of the calling thread.  Index arrays that live on the device (slots, positions, block tables) cannot be
+ *     checked by the host: the kernels range-check them, skip the offending row and set a device status word that
+ *     `gdn_device_status()` reads back.
+ *   - model constants: 16 heads, d_k = d_v = 128, mixed-qkv width 6144, in_proj row 8224 (qkv | z 2048 | b 16 | a 16),
+ *     one recurrent state = fp32 [16][128 value rows][128 key columns]
+ */
+#ifndef GDN_B200_H
+#define GDN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GDN_OK 0
+#define GDN_E_SHAPE (-1)
+#define GDN_E_DTYPE (-2)
+#define GDN_E_ALIGN (-3)
+#define GDN_E_INDEX (-4)
+#define GDN_E_LAUNCH (-5)
+#define GDN_E_TIMEOUT (-6)
+#define GDN_E_UNSUPPORTED (-7)
+#define GDN_E_NULL (-8)
+
+/* Library version (major*10000 + minor*100 + patch). */
+int gdn_version(void);
+
+/* Message of the last error returned to the calling thread ("" if none). */
+const char* gdn_last_error_string(void);
+
+/* Reads (and clears) the current device's status word: 0 = all device-side index checks passed since the last call,
+ * 1 = some kernel skipped a row because a slot / snapshot / page index was out of range.  Synchronises the device. */
+int gdn_device_status(int* status_host);
+
+/* compute_g and beta = sigmoid(b) with the reference's bf16 rounding points.
+ * Replaces: compute_g, qwen35/gated_delta.py:16-18; beta at qwen35/gated_delta.py:158; kernel form qwen35/kernels.py:511-515.
+ *   a, b     bf16, element (row r, head h) at a[r*a_stride + h] / b[r*b_stride + h]   (either may be NULL)
+ *   A_log, dt_bias   fp32 [H]
+ *   g, lg, beta      fp32 [n_rows, H] outputs: decay exp(lg), log-decay, beta           (any may be NULL) */
+int gdn_gates(const void* a, const void* b, long long a_stride, long long b_stride, const float* A_log, const float* dt_bias,
+              float* g, float* lg, float* beta, long long n_rows, int H, void* stream);
+
+/* q <- l2norm(q) * inv_scale^2, k <- l2norm(k) * inv_scale over rows of 128 bf16.
+ * Replaces: normalize_qk, qwen35/gated_delta.py:21-30 (kernel form qwen35/kernels.py:490-509). */
+int gdn_normalize_qk(const void* q, const void* k, void* q_out, void* k_out, long long n_rows, float inv_scale, float eps, void* stream);
+
+/* Sequential gated delta rule over T tokens.
+ * Replaces: gated_delta_update's kernel, qwen35/gated_delta.py:33-137,167-174.
+ *   q, k  bf16 [B,T,Hk,128];  v bf16 [B,T,Hv,Dv];  g, beta fp32 [B,T,Hv];  state_in fp32 [B,Hv,Dv,128] or NULL (zeros)
+ *   y     bf16 [B,T,Hv,Dv];   state_out fp32 [B,Hv,Dv,128]
+ * Errors: GDN_E_SHAPE unless Dk == 128, Dv % 16 == 0 and Hv % Hk == 0 (the reference raises ValueError, gated_delta.py:164-166). */
+int gdn_recurrent(const void* q, const void* k, const void* v, const float* g, const float* beta, const float* state_in, void* y,
+                  float* state_out, int B, int T, int Hk, int Hv, int Dk, int Dv, void* stream);
+
+/* Decode / speculative verify, solo flavour: M chained tokens, functional snapshot outputs.
+ * Replaces: deltanet, qwen35/kernels.py:555-567 (kernel :461-552).
+ *   proj bf16 [M, row_stride>=8224];  conv_snap bf16 [n_snap,3,6144];  conv_w bf16 [6144*4];  ssm_snap fp32 [n_snap,16,128,128]
+ *   sel int32[1] (device): snapshot the call starts from
+ *   y bf16 [M,2048];  conv_out bf16 [M,3,6144];  ssm_out fp32 [M,16,128,128]   (snapshot j = state after token j) */
+int gdn_deltanet(const void* proj, long long row_stride, const void* conv_snap, const void* conv_w, const float* A_log,
+                 const float* dt_bias, const float* ssm_snap, const int* sel, int n_snap, void* y, void* conv_out, float* ssm_out,
+                 int M, void* stream);
+
+/* Batched decode, one token for each of B slots, pools updated in place.
+ * Replaces: deltanet_b, qwen35/batch.py:128-135 (kernel :36-127).
+ *   conv_pool bf16 [n_slots*2,3,6144] (reads buffer pos&1 of the slot, writes the other);  ssm_pool fp32 [n_slots,16,128,128]
+ *   slots, pos int32 [B] (device);  y bf16 [B,2048] */
+int gdn_deltanet_b(const void* proj, long long row_stride, void* conv_pool, const void* conv_w, const float* A_log, const float* dt_bias,
+                   float* ssm_pool, const int* slots, const int* pos, int n_slots, void* y, int B, void* stream);
+
+/* Batched speculative verify, M chained tokens for each of B sequences over snapshot pools, in place.
+ * Replaces: deltanet_bm, qwen35/batch_spec.py:142-150 (kernel :45-141).
+ *   conv_pool bf16 [n_entries*2, M, 3, 6144];  ssm_pool fp32 [n_entries, M, 16,128,128]
+ *   sslots, sels, pars int32 [B] (device): pool entry, start snapshot, conv buffer read (the other one is written)
+ *   proj bf16 [B*M, row_stride];  y bf16 [B*M,2048] */
+int gdn_deltanet_bm(const void* proj, long long row_stride, void* conv_pool, const void* conv_w, const float* A_log, const float* dt_bias,
+                    float* ssm_pool, const int* sslots, const int* sels, const int* pars, int n_entries, void* y, int B, int M,
+                    void* stream);
+
+/* Bytes of fp32 workspace gqa_decode_paged needs for B sequences whose contexts are at most max_ctx tokens. */
+size_t gqa_decode_workspace_bytes(int B, int max_ctx);
+
+/* GQA decode attention (8 query heads, 2 KV heads, head_dim 256) over a paged bf16 KV cache, M <= 4 chained rows per
+ * sequence, new K/V rows appended in place.
+ * Replaces: attn_b, qwen35/batch.py:230-237 (kernel :141-227); the reference's slot pool [S+1,2,Lmax,256] is the case
+ * page_size = Lmax, max_pages = 1, block_table = slots.
+ *   q bf16 [B*M,8,256] (normed + roped, unscaled);  k_new, v_new bf16 [B*M,2,256]
+ *   k_pages, v_pages bf16 [n_pages,2,page_size,256];  block_table int32 [B,max_pages];  ctx_len int32 [B] (tokens cached)
+ *   out bf16 [B*M,8,256];  workspace: gqa_decode_workspace_bytes(B, max_ctx) bytes, 16-byte aligned
+ *   max_ctx: host-side upper bound of ctx_len (sizes the split-KV grid) */
+int gqa_decode_paged(const void* q, const void* k_new, const void* v_new, void* k_pages, void* v_pages, const int* block_table,
+                     const int* ctx_len, void* out, void* workspace, size_t workspace_bytes, int B, int M, int page_size,
+                     int max_pages, int n_pages, int max_ctx, void* stream);
+
+/* dst.flat[d0 + y*dstride + i] = src.flat[s0 + y*sstride + i] for i < n, y < ny; offsets in elements of elem_size (2 or 4) bytes.
+ * Replaces: blit, qwen35/batch.py:349-372. */
+int gdn_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,
+                   long long sstride, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GDN_B200_H */

@@ -1,0 +1,55 @@
+// Shared definitions for the GatedDeltaNet / GQA-decode kernels (sm_100a).
+//
+// Model constants follow the reference's Cfg (qwen35/model.py:35-60) and its kernel headers (qwen35/kernels.py:466):
+// 16 value heads, d_k = d_v = 128, mixed-qkv width 6144 = q 2048 | k 2048 | v 2048, in_proj row 8224 = qkv | z 2048 | b 16 | a 16.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "../../include/gdn_b200.h"
+
+namespace gdn {
+
+constexpr int HV = 16, DK = 128, DV = 128, KD = 2048, CD = 6144, PW = 8224;
+constexpr int STATE_ELEMS = HV * DV * DK;        // fp32 elements of one (sequence, layer) state
+
+// error codes (GDN_OK, GDN_E_*) come from the public header
+
+void set_error(const char* fmt, ...);             // stores a thread-local message for gdn_last_error_string()
+int check_launch(const char* what);               // cudaGetLastError -> GDN_E_LAUNCH (+ message)
+
+// ------------------------------------------------------------------------------------------------------------------
+// bf16 <-> fp32 and the "round after every op" bf16 math of the reference (qwen35/mslib.py:11-26)
+// ------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float bf(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+__device__ __forceinline__ float ldbf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+// mx.sigmoid on bf16: 1 / (1 + exp(|x|)), mirrored for x >= 0, rounding after each op
+__device__ __forceinline__ float sigmoid_bf16(float x) {
+    float y = bf(1.0f / bf(1.0f + bf(expf(fabsf(x)))));
+    return x < 0.0f ? y : bf(1.0f - y);
+}
+__device__ __forceinline__ float silu_bf16(float x) { return bf(x * sigmoid_bf16(x)); }
+// nn.softplus on bf16 = logaddexp(x, 0)
+__device__ __forceinline__ float softplus_bf16(float x) {
+    return bf(fmaxf(x, 0.0f) + bf(log1pf(bf(expf(-fabsf(x))))));
+}
+// log-decay of one token/head: -exp(A_log) * softplus_bf16(bf16(a + dt_bias))   (qwen35/kernels.py:511-513)
+__device__ __forceinline__ float log_decay(float expA, float a, float dtb) { return -expA * softplus_bf16(bf(a + dtb)); }
+
+__device__ __forceinline__ void unpack_bf16x4(uint2 u, float* f) {
+    f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+    f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+}  // namespace gdn

@@ -1,0 +1,63 @@
+// Argument blocks and host launchers of the kernels (one translation unit per kernel family).
+#pragma once
+#include "gdn_common.cuh"
+
+namespace gdn {
+
+// ---- gdn_decode.cu ----
+struct DecodeArgs {
+    const __nv_bfloat16* proj;        // [B*M, row_stride] rows: qkv 6144 | z 2048 | b 16 | a 16
+    long long row_stride;             // elements between consecutive proj rows
+    __nv_bfloat16* conv_pool;         // conv windows (layout depends on mode)
+    const __nv_bfloat16* conv_w;      // [6144*4] flat ch*4+tap, tap 3 = current token
+    const float* A_log;               // [16]
+    const float* dt_bias;             // [16]
+    float* ssm_pool;                  // fp32 states (layout depends on mode)
+    const int* i0;                    // mode 0: sel[1]      mode 1: slots[B]   mode 2: sslots[B]
+    const int* i1;                    //                     mode 1: pos[B]     mode 2: sels[B]
+    const int* i2;                    //                                        mode 2: pars[B]
+    __nv_bfloat16* y;                 // [B*M, 2048]
+    __nv_bfloat16* conv_out;          // mode 0: [M,3,6144]
+    float* ssm_out;                   // mode 0: [M,16,128,128]
+    int* status;                      // device word: set to 1 if an index was out of range (that row is skipped)
+    int B, M, mode, n_entries;        // n_entries: number of snapshots (mode 0) / slots (mode 1) / snapshot-pool entries (mode 2)
+};
+
+int launch_decode(const DecodeArgs& a, cudaStream_t stream);
+
+// ---- gdn_recurrent.cu ----
+struct RecurrentArgs {
+    const __nv_bfloat16 *q, *k, *v;   // q,k [B,T,Hk,128]; v [B,T,Hv,Dv]
+    const float *g, *beta;            // [B,T,Hv]
+    const float* state_in;            // [B,Hv,Dv,128] or nullptr (zeros)
+    __nv_bfloat16* y;                 // [B,T,Hv,Dv]
+    float* state_out;                 // [B,Hv,Dv,128]
+    int B, T, Hk, Hv, Dv;
+};
+
+int launch_recurrent(const RecurrentArgs& a, cudaStream_t stream);
+int launch_gates(const __nv_bfloat16* a, const __nv_bfloat16* b, long long a_stride, long long b_stride, const float* A_log,
+                 const float* dt_bias, float* g, float* lg, float* beta, long long n_rows, int H, cudaStream_t stream);
+int launch_normalize_qk(const __nv_bfloat16* q, const __nv_bfloat16* k, __nv_bfloat16* qo, __nv_bfloat16* ko, long long n_rows,
+                        float inv_scale, float eps, cudaStream_t stream);
+
+// ---- gqa_decode.cu ----
+struct AttnArgs {
+    const __nv_bfloat16 *q, *k_new, *v_new;     // q [B*M,8,256]; k_new, v_new [B*M,2,256]
+    __nv_bfloat16 *k_pages, *v_pages;           // [n_pages, 2, page_size, 256]
+    const int* block_table;                     // [B, max_pages]
+    const int* ctx_len;                         // [B] tokens already cached
+    __nv_bfloat16* out;                         // [B*M,8,256]
+    float* part;                                // workspace [B, 2, max_splits, PART_STRIDE]
+    int* status;
+    int B, M, page_size, max_pages, n_pages, split_keys, max_splits;
+};
+
+size_t gqa_workspace_bytes(int B, int max_ctx);
+int launch_gqa_decode(AttnArgs a, int max_ctx, cudaStream_t stream);
+
+// ---- state_copy.cu ----
+int launch_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,
+                      long long sstride, cudaStream_t st);
+
+}  // namespace gdn
