@@ -6,169 +6,321 @@
 // lives: `deltanet` (qwen35/kernels.py:461-567, functional snapshots), `deltanet_b` (qwen35/batch.py:36-135, slot pools
 // updated in place) and `deltanet_bm` (qwen35/batch_spec.py:45-150, snapshot pools updated in place).
 //
-// The kernel is bound by HBM traffic on the state (1 MiB read + M MiB written per sequence and layer).  Mapping:
-//   grid  = B x 16 heads x (128 / ROWS) value-row slices, 128 threads per block
-//   a state row (128 fp32 = 512 B) is spread over 8 lanes: lane l holds the float4s at columns 4l + 32i, i < 4, so a warp
-//   load instruction touches four complete 128-byte lines; the two 128-wide dot products per row are finished with three
-//   xor-shuffles inside the 8-lane group.  Each thread keeps its 16 (ROWS=16) or 32 (ROWS=32) state values in registers
-//   across the M tokens and streams one snapshot per token back with 128-bit stores.
-//   The conv/norm prologue of a token is computed once per block into shared memory (thread t = channel t of q and k).
+// The kernel is bound by HBM traffic on the state (1 MiB read + M MiB written per sequence and layer), so it is built as
+// a streaming pipeline:
+//   * the work list is every 32-row slice (16 KiB) of every (sequence, head) state; persistent blocks (three or four per SM) each take
+//     a contiguous range of it, so consecutive slices of a block usually belong to the same head;
+//   * a ring of shared-memory stages per block is kept full by one thread issuing 16 KiB bulk async copies (cp.async.bulk,
+//     completion on an mbarrier), so ~190 KiB of state reads are in flight per SM regardless of what the math is doing;
+//   * a slice is moved from shared memory to registers (a state row = 8 lanes x 4 float4, so each quarter-warp reads 128
+//     contiguous bytes), the stage is handed back to the copy engine, the M tokens are applied in registers and each snapshot
+//     is streamed out with 128-bit stores; the two 128-wide dot products per row end in three xor-shuffles;
+//   * the conv / l2norm / gate prologue of a head is computed once per head into shared memory (thread t = channel t of
+//     q, k and v) from inputs that were fetched into registers while the previous head was being processed.
 #include "gdn_common.cuh"
 #include "launchers.cuh"
+#include "sm100_prims.cuh"
 
 namespace gdn {
 
+constexpr int SLICE_ROWS = 32;
+constexpr int SLICES_PER_HEAD = DV / SLICE_ROWS;             // 4
+constexpr int SLICE_FLOATS = SLICE_ROWS * DK;                // 4096
+constexpr int SLICE_BYTES = SLICE_FLOATS * 4;                // 16 KiB
+// ring stages and resident blocks per SM, by the number of chained tokens a block keeps inputs for: the single-token decode
+// step needs many warps to cover the latency of its shuffle / FMA chains (4 blocks x 3 stages = 192 KiB of reads in flight per
+// SM); the multi-token verify is write-dominated and register-heavy (3 blocks x 4 stages)
+template <int MT> struct Tune { static constexpr int NST = MT == 1 ? 3 : 4; static constexpr int BLOCKS = MT == 1 ? 4 : (MT <= 4 ? 3 : 2); };
 
-template <int PASSES>
-__global__ void __launch_bounds__(128) gdn_decode_kernel(const DecodeArgs a) {
-    constexpr int ROWS = 16 * PASSES;
-    constexpr int NSL = DV / ROWS;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, sub = lane >> 3, l8 = lane & 7;
-    const int blk = blockIdx.x;
-    const int b = blk / (HV * NSL), hv = (blk / NSL) % HV, slice = blk % NSL;
-    const int row_base = slice * ROWS;
-    const int M = a.M;
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
 
-    // ---- where this sequence's state lives (qwen35/kernels.py:473-474, batch.py:47-54, batch_spec.py:57-65) ----
+// where one sequence's state and conv window live (qwen35/kernels.py:473-474, batch.py:47-54, batch_spec.py:57-65)
+struct SeqPtrs {
     const __nv_bfloat16* cs_in;
     __nv_bfloat16* cs_out;
     const float* st_in;
     float* st_out;
-    {
-        const int e = a.i0[a.mode == 0 ? 0 : b];
-        if (e < 0 || e >= a.n_entries) { if (tid == 0) atomicExch(a.status, 1); return; }
-        if (a.mode == 0) {
-            cs_in = a.conv_pool + (size_t)e * 3 * CD;
-            cs_out = a.conv_out;
-            st_in = a.ssm_pool + (size_t)e * STATE_ELEMS;
-            st_out = a.ssm_out;
-        } else if (a.mode == 1) {
-            const unsigned par = (unsigned)a.i1[b] & 1u;
-            cs_in = a.conv_pool + ((size_t)e * 2 + par) * 3 * CD;
-            cs_out = a.conv_pool + ((size_t)e * 2 + (par ^ 1u)) * 3 * CD;
-            st_in = a.ssm_pool + (size_t)e * STATE_ELEMS;
-            st_out = a.ssm_pool + (size_t)e * STATE_ELEMS;
-        } else {
-            const int sl = a.i1[b];
-            if (sl < 0 || sl >= M) { if (tid == 0) atomicExch(a.status, 1); return; }
-            const unsigned par = (unsigned)a.i2[b] & 1u;
-            cs_in = a.conv_pool + (((size_t)e * 2 + par) * M + sl) * 3 * CD;
-            cs_out = a.conv_pool + (((size_t)e * 2 + (par ^ 1u)) * M) * 3 * CD;
-            st_out = a.ssm_pool + (size_t)e * M * STATE_ELEMS;
-            st_in = st_out + (size_t)sl * STATE_ELEMS;
-        }
-    }
-    const __nv_bfloat16* pj = a.proj + (size_t)b * M * a.row_stride;
-    __nv_bfloat16* yb = a.y + (size_t)b * M * (HV * DV);
+    bool ok;
+};
 
-    __shared__ __align__(16) float sq[DK];
-    __shared__ __align__(16) float sk[DK];
-    __shared__ float sv[ROWS], sy[ROWS], sred[8];
-
-    // ---- state rows into registers (issued first: everything below overlaps with these loads) ----
-    float4 s[PASSES][4];
-    int rows[PASSES];
-#pragma unroll
-    for (int p = 0; p < PASSES; p++) {
-        rows[p] = row_base + (warp * PASSES + p) * 4 + sub;
-        const float* rp = st_in + ((size_t)hv * DV + rows[p]) * DK + l8 * 4;
-#pragma unroll
-        for (int i = 0; i < 4; i++) s[p][i] = *reinterpret_cast<const float4*>(rp + 32 * i);
+__device__ __forceinline__ SeqPtrs resolve(const DecodeArgs& a, int b) {
+    SeqPtrs p;
+    const int M = a.M;
+    const int e = a.i0[a.mode == 0 ? 0 : b];
+    p.ok = e >= 0 && e < a.n_entries;
+    const size_t es = p.ok ? (size_t)e : 0;
+    if (a.mode == 0) {
+        p.cs_in = a.conv_pool + es * 3 * CD;
+        p.cs_out = a.conv_out;
+        p.st_in = a.ssm_pool + es * STATE_ELEMS;
+        p.st_out = a.ssm_out;
+    } else if (a.mode == 1) {
+        const unsigned par = (unsigned)a.i1[b] & 1u;
+        p.cs_in = a.conv_pool + (es * 2 + par) * 3 * CD;
+        p.cs_out = a.conv_pool + (es * 2 + (par ^ 1u)) * 3 * CD;
+        p.st_in = a.ssm_pool + es * STATE_ELEMS;
+        p.st_out = a.ssm_pool + es * STATE_ELEMS;
+    } else {
+        int sl = a.i1[b];
+        if (sl < 0 || sl >= M) { p.ok = false; sl = 0; }
+        const unsigned par = (unsigned)a.i2[b] & 1u;
+        p.cs_in = a.conv_pool + ((es * 2 + par) * M + sl) * 3 * CD;
+        p.cs_out = a.conv_pool + ((es * 2 + (par ^ 1u)) * M) * 3 * CD;
+        p.st_out = a.ssm_pool + es * M * STATE_ELEMS;
+        p.st_in = p.st_out + (size_t)sl * STATE_ELEMS;
     }
+    return p;
+}
+
+// raw inputs of one thread's three channels (q, k, v channel `tid` of a head) for MT chained tokens
+// (kept as raw bf16 bits: converting at the point of use keeps the loads asynchronous when they are issued one head ahead)
+template <int MT>
+struct HeadInputs {
+    unsigned short win[3][3];    // stored window rows (t = -3, -2, -1)
+    unsigned short row[3][MT];   // new rows (t = 0 .. M-1)
+    uint2 w[3];                  // conv taps (4 bf16)
+    unsigned short a[MT], b[MT]; // gate inputs of the head
+};
+__device__ __forceinline__ unsigned short ldraw(const __nv_bfloat16* p) { return *reinterpret_cast<const unsigned short*>(p); }
+__device__ __forceinline__ float rawf(unsigned short u) { return __uint_as_float((uint32_t)u << 16); }
+
+template <int MT>
+__device__ __forceinline__ void fetch_head(const DecodeArgs& a, const SeqPtrs& sp, int b, int hv, int tid, HeadInputs<MT>& in) {
+    const __nv_bfloat16* pj = a.proj + (size_t)b * a.M * a.row_stride;
+#pragma unroll
+    for (int g = 0; g < 3; g++) {
+        const int ch = g * KD + hv * DK + tid;
+        in.w[g] = *reinterpret_cast<const uint2*>(a.conv_w + (size_t)ch * 4);
+#pragma unroll
+        for (int t = 0; t < 3; t++) in.win[g][t] = ldraw(sp.cs_in + t * CD + ch);
+#pragma unroll
+        for (int j = 0; j < MT; j++) in.row[g][j] = j < a.M ? ldraw(pj + (size_t)j * a.row_stride + ch) : (unsigned short)0;
+    }
+#pragma unroll
+    for (int j = 0; j < MT; j++) {
+        in.a[j] = j < a.M ? ldraw(pj + (size_t)j * a.row_stride + CD + KD + HV + hv) : (unsigned short)0;
+        in.b[j] = j < a.M ? ldraw(pj + (size_t)j * a.row_stride + CD + KD + hv) : (unsigned short)0;
+    }
+}
+
+template <int MT>
+__global__ void __launch_bounds__(128, Tune<MT>::BLOCKS) gdn_decode_kernel(const DecodeArgs a, int n_slices) {
+    constexpr int NST = Tune<MT>::NST;
+    extern __shared__ __align__(128) unsigned char dsmem[];
+    float* ring = reinterpret_cast<float*>(dsmem);                                  // [NST][SLICE_FLOATS]
+    float* sq = ring + NST * SLICE_FLOATS;                                          // [MT][128]
+    float* sk = sq + MT * DK;
+    float* sv = sk + MT * DK;
+    float* sred = sv + MT * DV;                                                     // [2*MT][4]
+    float* sgate = sred + 2 * MT * 4;                                               // [MT][2] (g, beta)
+    __shared__ uint64_t full_bar[NST];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, sub = lane >> 3, l8 = lane & 7;
+    const int M = a.M;
+    const int G = gridDim.x;
+    const int lo = (int)((long long)blockIdx.x * n_slices / G), hi = (int)((long long)(blockIdx.x + 1) * n_slices / G);
+    if (lo >= hi) return;
+
+    if (tid == 0) {
+        for (int s = 0; s < NST; s++) sm100::mbar_init(sm100::smem_addr(&full_bar[s]), 1);
+        sm100::fence_barrier_init();
+    }
+    __syncthreads();
+
+    auto issue = [&](int idx) {                         // thread 0: start the copy of slice `idx` into its ring stage
+        const int n = idx - lo, stage = n % NST;
+        const int b = idx / (HV * SLICES_PER_HEAD), hv = (idx / SLICES_PER_HEAD) % HV, sl = idx % SLICES_PER_HEAD;
+        const SeqPtrs sp = resolve(a, b);
+        const float* src = sp.st_in + ((size_t)hv * DV + sl * SLICE_ROWS) * DK;
+        const uint32_t bar = sm100::smem_addr(&full_bar[stage]);
+        sm100::mbar_expect_tx(bar, SLICE_BYTES);
+        bulk_load(sm100::smem_addr(ring + stage * SLICE_FLOATS), src, SLICE_BYTES, bar);
+    };
+    if (tid == 0)
+        for (int i = lo; i < hi && i < lo + NST; i++) issue(i);
 
     const float inv_scale = 0.08838834764831845f;          // 128^-1/2
     const float e2 = 1e-6f * inv_scale * inv_scale;
     const float sc_q = bf(inv_scale * inv_scale), sc_k = bf(inv_scale);
-    const float expA = expf(a.A_log[hv]);
-    const float dtb = a.dt_bias[hv];
 
-    // input row t of channel ch: t < 0 reads the stored window (qwen35/kernels.py:477-479)
-    auto inp = [&](int t, int ch) -> float {
-        return t < 0 ? ldbf(cs_in + (t + 3) * CD + ch) : ldbf(pj + (size_t)t * a.row_stride + ch);
-    };
-    auto conv = [&](int j, int ch) -> float {
-        const uint2 wb = *reinterpret_cast<const uint2*>(a.conv_w + (size_t)ch * 4);
-        float w[4];
-        unpack_bf16x4(wb, w);
-        float o = inp(j - 3, ch) * w[0];
-        o += inp(j - 2, ch) * w[1];
-        o += inp(j - 1, ch) * w[2];
-        o += inp(j, ch) * w[3];
-        return silu_bf16(bf(o));
-    };
-    auto put_window = [&](int j, int ch) {                 // conv snapshot j = rows j-2, j-1, j (qwen35/kernels.py:528-541)
+    HeadInputs<MT> nxt;
+    int have_b = -1, have_hv = -1;                         // head whose inputs sit in `nxt`
+    int cur_b = -1, cur_hv = -1;
+    SeqPtrs sp{};
+
+    for (int idx = lo; idx < hi; idx++) {
+        const int n = idx - lo, stage = n % NST;
+        const int b = idx / (HV * SLICES_PER_HEAD), hv = (idx / SLICES_PER_HEAD) % HV, sl = idx % SLICES_PER_HEAD;
+
+        if (b != cur_b || hv != cur_hv) {
+            // ---- prologue of a new head: conv + silu, l2norm, gates for the M tokens, conv-window snapshots ----
+            cur_b = b; cur_hv = hv;
+            sp = resolve(a, b);
+            if (!sp.ok && tid == 0) atomicExch(a.status, 1);
+            HeadInputs<MT> in;
+            if (have_b == b && have_hv == hv) in = nxt;
+            else fetch_head<MT>(a, sp, b, hv, tid, in);
+            // start fetching the next head of this block's range while this one is processed
+            {
+                const int nidx = (idx / SLICES_PER_HEAD + 1) * SLICES_PER_HEAD;
+                if (nidx < hi) {
+                    const int nb = nidx / (HV * SLICES_PER_HEAD), nhv = (nidx / SLICES_PER_HEAD) % HV;
+                    const SeqPtrs nsp = resolve(a, nb);
+                    fetch_head<MT>(a, nsp, nb, nhv, tid, nxt);
+                    have_b = nb; have_hv = nhv;
+                }
+            }
+            __syncthreads();                               // previous head's readers of sq/sk/sv are done
+            float qv[MT], kv[MT];
+            const float expA = expf(a.A_log[hv]);
+            const float dtb = a.dt_bias[hv];
 #pragma unroll
-        for (int t = 0; t < 3; t++) cs_out[((size_t)j * 3 + t) * CD + ch] = __float2bfloat16_rn(inp(j - 2 + t, ch));
-    };
-
-    for (int j = 0; j < M; j++) {
-        // ---- prologue: conv + silu for this head's q / k channels and this block's v rows ----
-        const int chq = hv * DK + tid, chk = KD + hv * DK + tid;
-        const float qv = conv(j, chq), kv = conv(j, chk);
-        const float qs_w = warp_sum(qv * qv), ks_w = warp_sum(kv * kv);
-        if (lane == 0) { sred[warp] = qs_w; sred[4 + warp] = ks_w; }
-        if (tid < ROWS) {
-            const int chv = 2 * KD + hv * DV + row_base + tid;
-            sv[tid] = conv(j, chv);
-            put_window(j, chv);
+            for (int j = 0; j < MT; j++) {
+                if (j < M) {
+                    float c[3];
+#pragma unroll
+                    for (int g = 0; g < 3; g++) {
+                        // input rows j-3 .. j of the channel: the stored window for t < 0, the new rows otherwise (kernels.py:477-484)
+                        float x[4], w[4];
+                        unpack_bf16x4(in.w[g], w);
+#pragma unroll
+                        for (int t = 0; t < 4; t++) {
+                            const int tt = j - 3 + t;
+                            x[t] = rawf(tt < 0 ? in.win[g][tt + 3] : in.row[g][tt < 0 ? 0 : tt]);
+                        }
+                        float o = x[0] * w[0];
+                        o += x[1] * w[1];
+                        o += x[2] * w[2];
+                        o += x[3] * w[3];
+                        c[g] = silu_bf16(bf(o));
+                    }
+                    qv[j] = c[0]; kv[j] = c[1];
+                    sv[j * DV + tid] = c[2];
+                    const float qs_w = warp_sum(c[0] * c[0]), ks_w = warp_sum(c[1] * c[1]);
+                    if (lane == 0) { sred[(2 * j) * 4 + warp] = qs_w; sred[(2 * j + 1) * 4 + warp] = ks_w; }
+                    if (tid == 0) {
+                        sgate[2 * j] = expf(log_decay(expA, rawf(in.a[j]), dtb));
+                        sgate[2 * j + 1] = sigmoid_bf16(rawf(in.b[j]));
+                    }
+                    // conv-window snapshot j = input rows j-2, j-1, j (kernels.py:528-541); written by the block that owns slice 0
+                    if (sl == 0 && sp.ok) {
+#pragma unroll
+                        for (int g = 0; g < 3; g++) {
+                            const int ch = g * KD + hv * DK + tid;
+#pragma unroll
+                            for (int t = 0; t < 3; t++) {
+                                const int tt = j - 2 + t;
+                                const unsigned short x = tt < 0 ? in.win[g][tt + 3] : in.row[g][tt < 0 ? 0 : tt];
+                                *reinterpret_cast<unsigned short*>(sp.cs_out + ((size_t)j * 3 + t) * CD + ch) = x;
+                            }
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < MT; j++) {
+                if (j < M) {
+                    const float qs = (sred[(2 * j) * 4] + sred[(2 * j) * 4 + 1]) + (sred[(2 * j) * 4 + 2] + sred[(2 * j) * 4 + 3]);
+                    const float ks = (sred[(2 * j + 1) * 4] + sred[(2 * j + 1) * 4 + 1]) + (sred[(2 * j + 1) * 4 + 2] + sred[(2 * j + 1) * 4 + 3]);
+                    const float qr = 1.0f / sqrtf(qs / (float)DK + e2);
+                    const float kr = 1.0f / sqrtf(ks / (float)DK + e2);
+                    sq[j * DK + tid] = bf(bf(qv[j] * qr) * sc_q);          // l2norm(q) / sqrt(128), rounded like kernels.py:504-509
+                    sk[j * DK + tid] = bf(bf(kv[j] * kr) * sc_k);
+                }
+            }
+            // (the barrier inside the slice step below orders these writes before their readers)
         }
-        if (slice == 0) { put_window(j, chq); put_window(j, chk); }
-        __syncthreads();
-        const float qs = (sred[0] + sred[1]) + (sred[2] + sred[3]);
-        const float ks = (sred[4] + sred[5]) + (sred[6] + sred[7]);
-        const float qr = 1.0f / sqrtf(qs / (float)DK + e2);
-        const float kr = 1.0f / sqrtf(ks / (float)DK + e2);
-        sq[tid] = bf(bf(qv * qr) * sc_q);                   // l2norm(q) / sqrt(128), rounded like the reference (kernels.py:504-509)
-        sk[tid] = bf(bf(kv * kr) * sc_k);
-        const float av = ldbf(pj + (size_t)j * a.row_stride + CD + KD + HV + hv);
-        const float g = expf(log_decay(expA, av, dtb));
-        const float beta = sigmoid_bf16(ldbf(pj + (size_t)j * a.row_stride + CD + KD + hv));
-        __syncthreads();
 
-        float4 kk[4], qq[4];
+        // ---- state slice: shared memory -> registers, then give the stage back to the copy engine ----
+        const bool arrived = sm100::mbar_wait(sm100::smem_addr(&full_bar[stage]), (uint32_t)(n / NST) & 1u);
+        float4 s[2][4];
+        int rows[2];
+        const float* sl_base = ring + stage * SLICE_FLOATS;
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            kk[i] = *reinterpret_cast<const float4*>(sk + l8 * 4 + 32 * i);
-            qq[i] = *reinterpret_cast<const float4*>(sq + l8 * 4 + 32 * i);
+        for (int p = 0; p < 2; p++) {
+            rows[p] = (warp * 2 + p) * 4 + sub;                            // row within the slice
+#pragma unroll
+            for (int i = 0; i < 4; i++) s[p][i] = *reinterpret_cast<const float4*>(sl_base + rows[p] * DK + l8 * 4 + 32 * i);
         }
-        float* so = st_out + (size_t)j * STATE_ELEMS;
-#pragma unroll
-        for (int p = 0; p < PASSES; p++) {
-            float kvm = 0.f;
+        __syncthreads();
+        if (tid == 0 && idx + NST < hi) issue(idx + NST);
+        if (!arrived) { if (tid == 0) atomicExch(a.status, 2); continue; }
+        if (!sp.ok) continue;
+
+        __nv_bfloat16* yb = a.y + (size_t)b * M * (HV * DV) + hv * DV + sl * SLICE_ROWS;
+        float* so_head = sp.st_out + ((size_t)hv * DV + sl * SLICE_ROWS) * DK;
+        for (int j = 0; j < M; j++) {
+            float4 kk[4], qq[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
-                s[p][i].x *= g; s[p][i].y *= g; s[p][i].z *= g; s[p][i].w *= g;
-                kvm += (s[p][i].x * kk[i].x + s[p][i].y * kk[i].y) + (s[p][i].z * kk[i].z + s[p][i].w * kk[i].w);
+                kk[i] = *reinterpret_cast<const float4*>(sk + j * DK + l8 * 4 + 32 * i);
+                qq[i] = *reinterpret_cast<const float4*>(sq + j * DK + l8 * 4 + 32 * i);
             }
-            kvm += __shfl_xor_sync(0xffffffffu, kvm, 1);
-            kvm += __shfl_xor_sync(0xffffffffu, kvm, 2);
-            kvm += __shfl_xor_sync(0xffffffffu, kvm, 4);
-            const float delta = (sv[rows[p] - row_base] - kvm) * beta;
-            float yv = 0.f;
-            float* rp = so + ((size_t)hv * DV + rows[p]) * DK + l8 * 4;
+            const float g = sgate[2 * j], beta = sgate[2 * j + 1];
+            float* so = so_head + (size_t)j * STATE_ELEMS;
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                s[p][i].x += kk[i].x * delta; s[p][i].y += kk[i].y * delta;
-                s[p][i].z += kk[i].z * delta; s[p][i].w += kk[i].w * delta;
-                yv += (s[p][i].x * qq[i].x + s[p][i].y * qq[i].y) + (s[p][i].z * qq[i].z + s[p][i].w * qq[i].w);
-                *reinterpret_cast<float4*>(rp + 32 * i) = s[p][i];
+            for (int p = 0; p < 2; p++) {
+                float kvm = 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    s[p][i].x *= g; s[p][i].y *= g; s[p][i].z *= g; s[p][i].w *= g;
+                    kvm += (s[p][i].x * kk[i].x + s[p][i].y * kk[i].y) + (s[p][i].z * kk[i].z + s[p][i].w * kk[i].w);
+                }
+                kvm += __shfl_xor_sync(0xffffffffu, kvm, 1);
+                kvm += __shfl_xor_sync(0xffffffffu, kvm, 2);
+                kvm += __shfl_xor_sync(0xffffffffu, kvm, 4);
+                const float delta = (sv[j * DV + sl * SLICE_ROWS + rows[p]] - kvm) * beta;
+                float yv = 0.f;
+                float* rp = so + rows[p] * DK + l8 * 4;
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    s[p][i].x += kk[i].x * delta; s[p][i].y += kk[i].y * delta;
+                    s[p][i].z += kk[i].z * delta; s[p][i].w += kk[i].w * delta;
+                    yv += (s[p][i].x * qq[i].x + s[p][i].y * qq[i].y) + (s[p][i].z * qq[i].z + s[p][i].w * qq[i].w);
+                    *reinterpret_cast<float4*>(rp + 32 * i) = s[p][i];
+                }
+                yv += __shfl_xor_sync(0xffffffffu, yv, 1);
+                yv += __shfl_xor_sync(0xffffffffu, yv, 2);
+                yv += __shfl_xor_sync(0xffffffffu, yv, 4);
+                if (l8 == 0) yb[(size_t)j * (HV * DV) + rows[p]] = __float2bfloat16_rn(yv);
             }
-            yv += __shfl_xor_sync(0xffffffffu, yv, 1);
-            yv += __shfl_xor_sync(0xffffffffu, yv, 2);
-            yv += __shfl_xor_sync(0xffffffffu, yv, 4);
-            if (l8 == 0) sy[rows[p] - row_base] = yv;
         }
-        __syncthreads();
-        if (tid < ROWS) yb[(size_t)j * (HV * DV) + hv * DV + row_base + tid] = __float2bfloat16_rn(sy[tid]);
     }
+}
+
+template <int MT>
+static int launch_mt(const DecodeArgs& a, cudaStream_t stream) {
+    static bool attr_set[64] = {};
+    static int sms[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    constexpr int NST = Tune<MT>::NST;
+    const int smem = NST * SLICE_BYTES + (3 * MT * DK + 2 * MT * 4 + 2 * MT) * (int)sizeof(float);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(gdn_decode_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return check_launch("gdn_decode smem attribute");
+        cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+        attr_set[dev] = true;
+    }
+    const int n_sm = (dev >= 0 && dev < 64 && sms[dev] > 0) ? sms[dev] : 148;
+    const int n_slices = a.B * HV * SLICES_PER_HEAD;
+    int grid = Tune<MT>::BLOCKS * n_sm;
+    if (grid > n_slices) grid = n_slices;
+    gdn_decode_kernel<MT><<<grid, 128, smem, stream>>>(a, n_slices);
+    return check_launch("gdn_decode");
 }
 
 int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
     if (a.B <= 0 || a.M <= 0) return GDN_OK;
-    // few sequences: 16-row slices double the block count so that one sequence still covers the GPU
-    if (a.B <= 8) gdn_decode_kernel<1><<<a.B * HV * 8, 128, 0, stream>>>(a);
-    else          gdn_decode_kernel<2><<<a.B * HV * 4, 128, 0, stream>>>(a);
-    return check_launch("gdn_decode");
+    if (a.M == 1) return launch_mt<1>(a, stream);
+    if (a.M <= 4) return launch_mt<4>(a, stream);
+    if (a.M <= 8) return launch_mt<8>(a, stream);
+    set_error("gdn_decode: M = %d chained tokens exceeds the supported 8", a.M);
+    return GDN_E_SHAPE;
 }
 
 }  // namespace gdn

@@ -13,8 +13,11 @@
 //   * GQA packing: the 4 query heads of a KV head times the M <= 4 chained rows form the 16 rows of a warp-level
 //     m16n8k16 bf16 MMA, so each K/V byte is read once for up to 16 query rows (at M = 4 plain FMAs could not keep up with
 //     HBM).  Each of the 4 warps owns 16 of the 64 keys of a tile and keeps its own online-softmax state.
-//   * K/V tiles (64 keys x 512 B) are gathered page by page with 16-byte cp.async into XOR-swizzled shared memory, two
-//     stages in flight (128 KiB per SM).
+//   * K/V tiles (64 keys x 512 B) are gathered page by page with 16-byte cp.async into XOR-swizzled shared memory, three
+//     stages (192 KiB per SM, two tiles in flight while one is consumed).  The page lookup of a tile's 64 keys is done once
+//     (one thread per key) and shared through shared memory.
+//   * the probabilities are fed to the P.V MMA as a bf16 hi + lo pair, so the result carries fp32-level accuracy like the
+//     reference's fp32 accumulation of exp_score * v.
 #include "gdn_common.cuh"
 #include "launchers.cuh"
 
@@ -24,8 +27,8 @@ constexpr int ATT_H = 8, ATT_KV = 2, ATT_D = 256, ATT_GQA = 4;
 constexpr int TK = 64;                          // keys per tile
 constexpr int ROWB = ATT_D * 2;                 // bytes per key row (512)
 constexpr int TILE_BYTES = TK * ROWB;           // 32 KiB
-constexpr int ATT_STAGES = 2;
-constexpr int ATT_SMEM = 16 * ROWB + ATT_STAGES * 2 * TILE_BYTES;     // Q (8 KiB) + stages x (K + V)
+constexpr int ATT_STAGES = 3;
+constexpr int ATT_SMEM = 16 * ROWB + ATT_STAGES * 2 * TILE_BYTES + ATT_STAGES * TK * 8;     // Q (8 KiB) + stages x (K + V) + row offsets
 constexpr int PART_STRIDE = 16 * ATT_D + 32;    // floats per (sequence, kv head, split): O[16][256] + (m, l)[16]
 
 
@@ -91,27 +94,34 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a)
         *reinterpret_cast<uint4*>(smem + swz(r, c)) = v;
     }
 
-    auto load_tile = [&](int t, int stage) {
+    // element offset of every key row of a tile (or -1 = zero fill), looked up once per tile by threads 0..63
+    long long* row_off = reinterpret_cast<long long*>(smem + 16 * ROWB + ATT_STAGES * 2 * TILE_BYTES);
+    auto plan_tile = [&](int t, int stage) {
+        if (tid < TK) {
+            long long off = -1;
+            if (t < ctx_tiles) {
+                const int key = k_begin + t * TK + tid;
+                if (key < k_end) {
+                    const int page = table[key / a.page_size];
+                    if (page >= 0 && page < a.n_pages) off = (((long long)page * ATT_KV + kvh) * a.page_size + key % a.page_size) * ATT_D;
+                }
+            } else if (tid < M) {
+                off = -2 - ((((long long)b * M + tid) * ATT_KV + kvh) * ATT_D);          // new rows live in k_new / v_new
+            }
+            row_off[stage * TK + tid] = off;
+        }
+    };
+    auto load_tile = [&](int stage) {
         const uint32_t dK = sKV + stage * 2 * TILE_BYTES, dV = dK + TILE_BYTES;
         const int c = tid & 31;
 #pragma unroll 4
         for (int i = 0; i < 16; i++) {
             const int r = (tid >> 5) + 4 * i;
+            const long long off = row_off[stage * TK + r];
             const __nv_bfloat16 *srcK = a.k_pages, *srcV = a.v_pages;
             int bytes = 0;
-            if (t < ctx_tiles) {
-                const int key = k_begin + t * TK + r;
-                if (key < k_end) {
-                    const int page = table[key / a.page_size];
-                    if (page >= 0 && page < a.n_pages) {
-                        const size_t off = (((size_t)page * ATT_KV + kvh) * a.page_size + key % a.page_size) * ATT_D;
-                        srcK = a.k_pages + off; srcV = a.v_pages + off; bytes = 16;
-                    }
-                }
-            } else if (r < M) {
-                const size_t off = (((size_t)b * M + r) * ATT_KV + kvh) * ATT_D;
-                srcK = a.k_new + off; srcV = a.v_new + off; bytes = 16;
-            }
+            if (off >= 0) { srcK = a.k_pages + off; srcV = a.v_pages + off; bytes = 16; }
+            else if (off <= -2) { srcK = a.k_new + (-2 - off); srcV = a.v_new + (-2 - off); bytes = 16; }
             cp_async16(dK + swz(r, c), reinterpret_cast<const uint4*>(srcK) + (bytes ? c : 0), bytes);
             cp_async16(dV + swz(r, c), reinterpret_cast<const uint4*>(srcV) + (bytes ? c : 0), bytes);
         }
@@ -123,13 +133,19 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a)
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const float sc = 0.0625f * 1.4426950408889634f;          // 256^-1/2 (qwen35/batch.py:176), scores kept in log2 units
 
-    load_tile(0, 0);
-    cp_async_commit();
-    for (int t = 0; t < ntiles; t++) {
-        const int stage = t & 1;
-        if (t + 1 < ntiles) load_tile(t + 1, stage ^ 1);
+    // prologue: plan the first three tiles, start the first two
+    for (int t = 0; t < ATT_STAGES && t < ntiles; t++) plan_tile(t, t);
+    __syncthreads();
+    for (int t = 0; t < ATT_STAGES - 1; t++) {
+        if (t < ntiles) load_tile(t);
         cp_async_commit();
-        cp_async_wait<1>();
+    }
+    for (int t = 0; t < ntiles; t++) {
+        const int stage = t % ATT_STAGES;
+        // tile t+2 goes into the stage that tile t-1 used (all warps left it at the barrier that ended iteration t-1)
+        if (t + ATT_STAGES - 1 < ntiles) load_tile((t + ATT_STAGES - 1) % ATT_STAGES);
+        cp_async_commit();
+        cp_async_wait<ATT_STAGES - 1>();
         __syncthreads();
 
         const bool new_tile = t >= ctx_tiles;
@@ -170,7 +186,7 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a)
                 m_run[h] = mn;
                 l_run[h] *= alpha[h];
             }
-            uint32_t pf[4];
+            uint32_t pf[4], pl[4];
             {
                 float p[2][4];
 #pragma unroll
@@ -183,6 +199,13 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a)
                     }
                 pf[0] = pack_bf16x2(p[0][0], p[0][1]); pf[1] = pack_bf16x2(p[0][2], p[0][3]);
                 pf[2] = pack_bf16x2(p[1][0], p[1][1]); pf[3] = pack_bf16x2(p[1][2], p[1][3]);
+                // low parts: p - bf16(p), exact in fp32, then rounded to bf16 (16 significand bits in total)
+#pragma unroll
+                for (int n = 0; n < 2; n++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) p[n][e] -= bf(p[n][e]);
+                pl[0] = pack_bf16x2(p[0][0], p[0][1]); pl[1] = pack_bf16x2(p[0][2], p[0][3]);
+                pl[2] = pack_bf16x2(p[1][0], p[1][1]); pl[3] = pack_bf16x2(p[1][2], p[1][3]);
             }
 #pragma unroll
             for (int n = 0; n < 32; n++) { o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1]; }
@@ -192,8 +215,13 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a)
                 ldsm_x4_t(tV + swz(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * nb + (lane >> 4)), vf);
                 mma_bf16(o[2 * nb], pf, vf[0], vf[1]);
                 mma_bf16(o[2 * nb + 1], pf, vf[2], vf[3]);
+                mma_bf16(o[2 * nb], pl, vf[0], vf[1]);
+                mma_bf16(o[2 * nb + 1], pl, vf[2], vf[3]);
             }
         }
+        // this tile's row offsets were consumed two iterations ago: plan tile t+3 into the same slot; the barrier below orders
+        // the plan before the load at the top of iteration t+1
+        if (t + ATT_STAGES < ntiles) plan_tile(t + ATT_STAGES, stage);
         __syncthreads();
     }
     cp_async_wait<0>();
