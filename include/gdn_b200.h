@@ -65,6 +65,21 @@ int gdn_normalize_qk(const void* q, const void* k, void* q_out, void* k_out, lon
 int gdn_recurrent(const void* q, const void* k, const void* v, const float* g, const float* beta, const float* state_in, void* y,
                   float* state_out, int B, int T, int Hk, int Hv, int Dk, int Dv, void* stream);
 
+/* Chunked prefill (chunk 64, tcgen05 tensor cores) over a packed varlen batch, with optional resume from a cached state.
+ * Replaces: gdn_chunked, qwen35/gdn_nax.py:413-426 (phase A :71-143, phase B :224-358).  The reference handles one sequence
+ * per call (B = 1); cu_seqlens packing and init_idx are the additive extension for ragged batches and prefix-cache resume.
+ *   q, k, v  bf16 [total_T, H, 128] (q, k already normalised; q scaled by 128^-1/2), 16-byte aligned
+ *   lg, beta fp32 [total_T, H]: log-decay and beta of every token and head (see gdn_gates)
+ *   cu_seqlens int32 [n_seq+1] (device): sequence s owns tokens [cu_seqlens[s], cu_seqlens[s+1])
+ *   init_state fp32 [*, H, 128, 128] or NULL (zero states); init_idx int32 [n_seq] (device) or NULL: row of init_state the
+ *              sequence resumes from, negative = zero state; with init_state != NULL and init_idx == NULL row s is used
+ *   y bf16 [total_T, H, 128];  final_state fp32 [n_seq, H, 128, 128]
+ *   heads [head_lo, head_hi) are computed (head-group sharding of one long sequence); the others are not touched
+ * Errors: GDN_E_SHAPE for bad sizes, GDN_E_ALIGN, GDN_E_UNSUPPORTED if the driver lacks tensor-map support. */
+int gdn_prefill_chunked(const void* q, const void* k, const void* v, const float* lg, const float* beta, const int* cu_seqlens,
+                        const float* init_state, const int* init_idx, void* y, float* final_state, int n_seq, long long total_T, int H,
+                        int head_lo, int head_hi, void* stream);
+
 /* Decode / speculative verify, solo flavour: M chained tokens, functional snapshot outputs.
  * Replaces: deltanet, qwen35/kernels.py:555-567 (kernel :461-552).
  *   proj bf16 [M, row_stride>=8224];  conv_snap bf16 [n_snap,3,6144];  conv_w bf16 [6144*4];  ssm_snap fp32 [n_snap,16,128,128]

@@ -93,6 +93,28 @@ int gdn_recurrent(const void* q, const void* k, const void* v, const float* g, c
     return launch_recurrent(a, static_cast<cudaStream_t>(stream));
 }
 
+int gdn_prefill_chunked(const void* q, const void* k, const void* v, const float* lg, const float* beta, const int* cu_seqlens,
+                        const float* init_state, const int* init_idx, void* y, float* final_state, int n_seq, long long total_T, int H,
+                        int head_lo, int head_hi, void* stream) {
+    REQUIRE(q && k && v && lg && beta && cu_seqlens && y && final_state, GDN_E_NULL, "gdn_prefill_chunked: null pointer");
+    REQUIRE(n_seq >= 0 && total_T >= 0 && total_T < (1ll << 31) && H > 0 && H <= 65535, GDN_E_SHAPE, "gdn_prefill_chunked: n_seq=%d total_T=%lld H=%d",
+            n_seq, total_T, H);
+    REQUIRE(head_lo >= 0 && head_lo <= head_hi && head_hi <= H, GDN_E_SHAPE, "gdn_prefill_chunked: head range [%d, %d) outside [0, %d)", head_lo,
+            head_hi, H);
+    REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(init_state) && aligned16(final_state), GDN_E_ALIGN,
+            "gdn_prefill_chunked: q / k / v / states must be 16-byte aligned");
+    if (n_seq == 0 || head_lo == head_hi) return GDN_OK;
+    PrefillArgs a{};
+    a.lg = lg; a.beta = beta; a.cu_seqlens = cu_seqlens; a.init_state = init_state; a.init_idx = init_idx;
+    a.y = static_cast<__nv_bfloat16*>(y); a.final_state = final_state;
+    a.n_seq = n_seq; a.H = H; a.head_lo = head_lo; a.n_heads = head_hi - head_lo; a.total_T = total_T;
+    a.status = status_ptr();
+    REQUIRE(a.status, GDN_E_LAUNCH, "gdn_prefill_chunked: no CUDA device");
+    if (total_T == 0) total_T = 1;          // a tensor map needs a non-empty extent; empty sequences never issue a copy
+    a.total_T = total_T;
+    return launch_prefill(q, k, v, a, static_cast<cudaStream_t>(stream));
+}
+
 static int decode_common(DecodeArgs& a, void* stream, const char* who) {
     REQUIRE(a.proj && a.conv_pool && a.conv_w && a.A_log && a.dt_bias && a.ssm_pool && a.i0 && a.y, GDN_E_NULL, "%s: null pointer", who);
     REQUIRE(a.row_stride >= PW, GDN_E_SHAPE, "%s: proj row stride %lld < 8224", who, a.row_stride);

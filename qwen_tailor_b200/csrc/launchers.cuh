@@ -56,6 +56,21 @@ struct AttnArgs {
 size_t gqa_workspace_bytes(int B, int max_ctx);
 int launch_gqa_decode(AttnArgs a, int max_ctx, cudaStream_t stream);
 
+// ---- gdn_prefill_sm100.cu ----
+struct PrefillArgs {
+    const float* lg;                  // [total_T, H] log-decay per token and head
+    const float* beta;                // [total_T, H]
+    const int* cu_seqlens;            // [n_seq + 1] token offsets of the packed sequences
+    const float* init_state;          // [*, H, 128, 128] fp32 or nullptr (all sequences start from zero)
+    const int* init_idx;              // [n_seq] row of init_state per sequence (< 0 = zero state) or nullptr (row = sequence)
+    __nv_bfloat16* y;                 // [total_T, H, 128]
+    float* final_state;               // [n_seq, H, 128, 128]
+    int* status;
+    int n_seq, H, head_lo, n_heads;
+    long long total_T;
+};
+int launch_prefill(const void* q, const void* k, const void* v, const PrefillArgs& a, cudaStream_t stream);
+
 // ---- state_copy.cu ----
 int launch_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,
                       long long sstride, cudaStream_t st);
