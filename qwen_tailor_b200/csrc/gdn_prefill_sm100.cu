@@ -12,18 +12,22 @@
 //
 // Mapping.  One block = one (sequence, head) chain; the chain over chunks is serial, heads / sequences / layers are the
 // parallel axis.  Every product is computed TRANSPOSED so that the 128 value rows of the head are the M dimension of a
-// full-rate M = 128 MMA and the TMEM lane of a thread is "its" value row for the whole kernel:
-//     G    [128 x 64]  = [K; Q] K^T          rows 0-63 = K K^T, rows 64-127 = Q K^T (K and Q tiles are stacked in smem)
-//     P1^T [dv x 64]   = S0 K^T,  P2^T = S0 Q^T                       A = S0 (bf16 hi + lo) from TMEM
-//     D^T  [dv x 64]   = Z^T Tb^T,  Z^T = V^T - P1^T diag(gamma)      A = Z^T (hi + lo) from TMEM, B = Tb (hi + lo) in smem
-//     AD^T [dv x 64]   = D^T A^T                                      A = D^T (hi + lo) from TMEM, B = A (hi + lo) in smem
-//     S    [dv x 128] += Dp^T K,  Dp = diag(dec) D                    A = Dp^T (hi + lo) in smem, B = K read MN-major
-// The fp32 state lives in TMEM for the whole sequence.  Every operand that is derived from fp32 data (S, Z, D, Dp, Tb, A) is
-// fed to the bf16 MMA as an exact hi + lo pair (16 significand bits), which keeps the final state within 1e-4 of fp64; K, Q
-// and V are bf16 already.  (I + L)^-1 is an exact fp32 forward substitution (one column per thread), as in the reference
-// (qwen35/gdn_nax.py:118-141): the tensor-core products with T are the "solve products".
-// K/Q/V chunks arrive by TMA (128-byte swizzle, no multicast), double buffered; rows of a partial last chunk are zeroed in
-// shared memory so that a packed neighbour sequence can never leak in.
+// full-rate M = 128 MMA and a TMEM lane is one value row for the whole kernel:
+//     G    [128 x 64]  = [K; Q] K^T            rows 0-63 = K K^T, rows 64-127 = Q K^T (K and Q tiles are stacked in smem)
+//     P1^T [dv x 64]   = S0 K^T,  P2^T = S0 Q^T                         A = S0 (bf16 hi + lo) from TMEM
+//     D^T  [dv x 64]   = V^T Tb^T + P1^T Tg^T,  Tg = -Tb diag(gamma)    A = V read MN-major from smem / P1^T (hi + lo) from TMEM
+//     AD^T [dv x 64]   = D^T A^T                                        A = D^T (hi + lo) from TMEM, B = A (hi + lo) in smem
+//     S    [dv x 128] += Dp^T K,  Dp = diag(dec) D                      A = Dp^T (hi + lo) in smem, B = K read MN-major
+// The fp32 state lives in TMEM for the whole sequence.  Every operand that is derived from fp32 data (S, P1, D, Dp, Tb, Tg, A)
+// is fed to the bf16 MMA as an exact hi + lo pair (16 significand bits), which keeps the final state within 1e-4 of fp64; K,
+// Q and V are bf16 already.  (I + L)^-1 is an exact fp32 forward substitution (one column per thread), as in the reference
+// (qwen35/gdn_nax.py:118-141); the tensor-core products with T are the "solve products".
+//
+// Roles (416 threads): warps 0-3 build everything that does not depend on the state (gates, L, A, the solve, Tb / Tg) and write
+// y; warps 4-11 do the state-dependent passes between MMAs (two warps per TMEM lane quadrant, half of the columns each); lane 0
+// of warp 12 issues every tcgen05.mma.  The groups hand over through mbarriers; K/Q/V chunks arrive by TMA (128-byte swizzle,
+// no multicast), double buffered; rows of a partial last chunk are zeroed in shared memory so that a packed neighbour
+// sequence can never leak in.  Every wait is bounded: a wait that gives up sets the device status word and the block leaves.
 #include <cuda.h>
 #include "gdn_common.cuh"
 #include "launchers.cuh"
@@ -34,18 +38,22 @@ namespace gdn {
 using namespace sm100;
 
 constexpr int CH = 64;                               // chunk length
+constexpr int PF_THREADS = 416;
 // ---- shared memory map (bytes from a 1024-aligned base) ----
 constexpr int SM_STAGE = 48 * 1024;                  // per stage: [K_h0 | Q_h0 | K_h1 | Q_h1] (4 x 8 KiB) + [V_h0 | V_h1] (2 x 8 KiB)
 constexpr int SM_V = 32 * 1024;                      // offset of V inside a stage
-constexpr int SM_TB_HI = 2 * SM_STAGE;               // Tb hi / lo, A hi / lo: [64][64] bf16, K-major, 8 KiB each
+constexpr int SM_TB_HI = 2 * SM_STAGE;               // Tb, Tg, A as bf16 hi / lo: [64][64], K-major, 8 KiB each
 constexpr int SM_TB_LO = SM_TB_HI + 8192;
-constexpr int SM_A_HI = SM_TB_LO + 8192;
+constexpr int SM_TG_HI = SM_TB_LO + 8192;
+constexpr int SM_TG_LO = SM_TG_HI + 8192;
+constexpr int SM_A_HI = SM_TG_LO + 8192;
 constexpr int SM_A_LO = SM_A_HI + 8192;
 constexpr int SM_DP_HI = SM_A_LO + 8192;             // Dp^T hi / lo: [128][64] bf16, K-major, 16 KiB each
 constexpr int SM_DP_LO = SM_DP_HI + 16384;
-constexpr int SM_L = SM_DP_LO + 16384;               // L fp32 [64][LSTRIDE]
+constexpr int SM_L = SM_DP_LO + 16384;               // L fp32, column-major: Lt[j][i] = L[i][j], [64][LSTRIDE]
 constexpr int LSTRIDE = 68;
-constexpr int SM_GATES = SM_L + 64 * LSTRIDE * 4;    // Lc, gamma, dec, beta [64] fp32 each + scratch
+constexpr int SM_T = SM_L + 64 * LSTRIDE * 4;        // T fp32 [64][LSTRIDE]; the same bytes stage y [64][128] bf16 for the epilogue
+constexpr int SM_GATES = SM_T + 64 * LSTRIDE * 4;    // Lc2, gamma, -gamma, dec, beta: [64] fp32 each
 constexpr int SM_TOTAL = SM_GATES + 5 * 256 + 64;
 // ---- tensor memory map (columns) ----
 constexpr uint32_t TM_S = 0;                         // fp32 state, pre-scaled by the coming chunk's gamma_C   [128 cols]
@@ -53,72 +61,99 @@ constexpr uint32_t TM_SHI = 128, TM_SLO = 192;       // bf16 pairs of the unscal
 constexpr uint32_t TM_G = 256;                       // [K;Q] K^T, later A D                                    [64]
 constexpr uint32_t TM_P1 = 320;                      // S0 K^T, later D^T                                       [64]
 constexpr uint32_t TM_P2 = 384;                      // S0 Q^T                                                  [64]
-constexpr uint32_t TM_ZHI = 448, TM_ZLO = 480;       // Z^T, later D^T, as bf16 pairs                           [32 + 32]
+constexpr uint32_t TM_ZHI = 448, TM_ZLO = 480;       // P1^T, later D^T, as bf16 pairs                          [32 + 32]
+// ---- mbarriers ----
+enum { B_KQV0 = 0, B_KQV1, B_INPUTS, B_GDONE, B_TB, B_SREADY, B_P1DONE, B_ZREADY, B_DDONE, B_DPREADY, B_SDONE, B_YDONE, B_AGRP, B_COUNT };
+
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr uint32_t WAIT_LIMIT = 2000000u;
+
+__device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 
 __device__ __forceinline__ void split_pack(float x0, float x1, uint32_t& hi, uint32_t& lo) {
-    const float h0 = bf(x0), h1 = bf(x1);
-    hi = pack_bf16x2(h0, h1);
-    lo = pack_bf16x2(x0 - h0, x1 - h1);
+    hi = pack_bf16x2(x0, x1);
+    lo = pack_bf16x2(x0 - __uint_as_float(hi << 16), x1 - __uint_as_float(hi & 0xffff0000u));
 }
 
-// exact forward substitution for column j of T = (I + L)^-1, rows I0..63 (rows above I0 are zero for columns >= I0)
-template <int I0>
-__device__ __forceinline__ void solve_column(const float* Lm, int j, float (&x)[64]) {
+// Exact forward substitution for column j of T = (I + L)^-1 (x_i = [i == j] - sum_{m < i} L[i][m] x_m), 16 rows at a time:
+// the contribution of all earlier rows is a rolled loop (x_m is read back from this thread's own column of Tm, L comes as the
+// column-major copy Lt[m][i] so that 16 rows of one column are four broadcast float4 loads), the 16 x 16 triangle inside the
+// block is unrolled.  Sixteen independent accumulators keep the FMA pipe busy and the code stays small enough for the
+// instruction cache (a fully unrolled 64 x 64 substitution does not).  B0 = first block with a non-zero row for this warp.
+template <int B0>
+__device__ __forceinline__ void solve_column(const float* Lt, float* Tm, int j) {
 #pragma unroll
-    for (int i = 0; i < I0; i++) x[i] = 0.f;
+    for (int i = 0; i < 16 * B0; i++) Tm[i * LSTRIDE + j] = 0.f;
 #pragma unroll
-    for (int i = I0; i < 64; i++) {
-        float acc = (i == j) ? 1.f : 0.f;
+    for (int b = B0; b < 4; b++) {
+        float acc[16];
 #pragma unroll
-        for (int m4 = I0; m4 < i; m4 += 4) {
-            const float4 l = *reinterpret_cast<const float4*>(Lm + i * LSTRIDE + m4);
-            acc -= l.x * x[m4];
-            if (m4 + 1 < i) acc -= l.y * x[m4 + 1];
-            if (m4 + 2 < i) acc -= l.z * x[m4 + 2];
-            if (m4 + 3 < i) acc -= l.w * x[m4 + 3];
+        for (int ii = 0; ii < 16; ii++) acc[ii] = (16 * b + ii == j) ? 1.f : 0.f;
+#pragma unroll 2
+        for (int m = 16 * B0; m < 16 * b; m++) {
+            const float xm = Tm[m * LSTRIDE + j];
+            const float4* lp = reinterpret_cast<const float4*>(Lt + m * LSTRIDE + 16 * b);
+#pragma unroll
+            for (int v4 = 0; v4 < 4; v4++) {
+                const float4 l = lp[v4];
+                acc[4 * v4] -= l.x * xm; acc[4 * v4 + 1] -= l.y * xm; acc[4 * v4 + 2] -= l.z * xm; acc[4 * v4 + 3] -= l.w * xm;
+            }
         }
-        x[i] = acc;
+#pragma unroll
+        for (int ii = 0; ii < 16; ii++) {
+            const float x = acc[ii];
+            Tm[(16 * b + ii) * LSTRIDE + j] = x;
+            const float* lrow = Lt + (16 * b + ii) * LSTRIDE + 16 * b;
+#pragma unroll
+            for (int kk = ii + 1; kk < 16; kk++) acc[kk] -= lrow[kk] * x;
+        }
     }
 }
 
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(PF_THREADS, 1)
 gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const PrefillArgs a) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    __shared__ uint64_t bars[3];
+    __shared__ uint64_t bars[B_COUNT];
     __shared__ uint32_t tmem_slot;
-    __shared__ float s_red[8];
+    __shared__ float s_scan[4];
+    __shared__ int s_abort;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.x / a.n_heads, h = a.head_lo + blockIdx.x % a.n_heads;
     const int t_begin = a.cu_seqlens[seq], t_end = a.cu_seqlens[seq + 1];
     const int len = t_end - t_begin;
-    float* fin = a.final_state + ((size_t)seq * a.H + h) * DV * DK + (size_t)tid * DK;
-    const float* init = nullptr;
+    const float* init_head = nullptr;
     if (a.init_state) {
         const int ii = a.init_idx ? a.init_idx[seq] : seq;
-        if (ii >= 0) init = a.init_state + ((size_t)ii * a.H + h) * DV * DK + (size_t)tid * DK;
+        if (ii >= 0) init_head = a.init_state + ((size_t)ii * a.H + h) * DV * DK;
     }
+    float* fin_head = a.final_state + ((size_t)seq * a.H + h) * DV * DK;
     if (len <= 0 || t_begin < 0 || t_end > a.total_T) {
-        // nothing to compute: the state passes through unchanged
         if (len < 0 || t_begin < 0 || t_end > a.total_T) { if (tid == 0) atomicExch(a.status, 1); return; }
-        for (int c = 0; c < DK; c += 4)
-            *reinterpret_cast<float4*>(fin + c) = init ? *reinterpret_cast<const float4*>(init + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = tid * 4; i < DV * DK; i += PF_THREADS * 4)       // nothing to compute: the state passes through unchanged
+            *reinterpret_cast<float4*>(fin_head + i) = init_head ? *reinterpret_cast<const float4*>(init_head + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         return;
     }
     const int nchunks = (len + CH - 1) / CH;
 
     const uint32_t sbase = smem_addr(smem);
-    const uint32_t bar_tma0 = smem_addr(&bars[0]), bar_tma1 = smem_addr(&bars[1]), bar_mma = smem_addr(&bars[2]);
+    auto bar = [&](int i) -> uint32_t { return smem_addr(&bars[i]); };
     float* Lm = reinterpret_cast<float*>(smem + SM_L);
-    float* s_Lc = reinterpret_cast<float*>(smem + SM_GATES);
+    float* Tm = reinterpret_cast<float*>(smem + SM_T);
+    float* s_Lc = reinterpret_cast<float*>(smem + SM_GATES);          // cumulative log2-decay
     float* s_gam = s_Lc + 64;
-    float* s_dec = s_gam + 64;
+    float* s_ngam = s_gam + 64;
+    float* s_dec = s_ngam + 64;
     float* s_beta = s_dec + 64;
 
     if (tid == 0) {
-        mbar_init(bar_tma0, 1); mbar_init(bar_tma1, 1); mbar_init(bar_mma, 1);
+        mbar_init(bar(B_KQV0), 1); mbar_init(bar(B_KQV1), 1);
+        mbar_init(bar(B_INPUTS), 4); mbar_init(bar(B_TB), 4); mbar_init(bar(B_AGRP), 4);
+        mbar_init(bar(B_SREADY), 8); mbar_init(bar(B_ZREADY), 8); mbar_init(bar(B_DPREADY), 8);
+        mbar_init(bar(B_GDONE), 1); mbar_init(bar(B_P1DONE), 1); mbar_init(bar(B_DDONE), 1); mbar_init(bar(B_SDONE), 1); mbar_init(bar(B_YDONE), 1);
+        s_abort = 0;
         fence_barrier_init();
         tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
     }
@@ -127,172 +162,339 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tb = tmem_slot;
-    const uint32_t tl = tb + ((uint32_t)(warp * 32) << 16);          // this warp's 32 lanes
 
-    auto issue_tma = [&](int c) {                                    // thread 0: K, Q, V of chunk c -> stage c & 1
+    auto issue_tma = [&](int c) {                                    // one thread: K, Q, V of chunk c -> stage c & 1
         const uint32_t st = sbase + (c & 1) * SM_STAGE;
-        const uint32_t bar = (c & 1) ? bar_tma1 : bar_tma0;
+        const uint32_t kb = bar((c & 1) ? B_KQV1 : B_KQV0);
         const int t0 = t_begin + c * CH;
-        mbar_expect_tx(bar, 6 * 8192);
-        tma_load_3d(st, &tmK, bar, 0, h, t0);
-        tma_load_3d(st + 8192, &tmQ, bar, 0, h, t0);
-        tma_load_3d(st + 16384, &tmK, bar, 64, h, t0);
-        tma_load_3d(st + 24576, &tmQ, bar, 64, h, t0);
-        tma_load_3d(st + SM_V, &tmV, bar, 0, h, t0);
-        tma_load_3d(st + SM_V + 8192, &tmV, bar, 64, h, t0);
+        mbar_expect_tx(kb, 6 * 8192);
+        tma_load_3d(st, &tmK, kb, 0, h, t0);
+        tma_load_3d(st + 8192, &tmQ, kb, 0, h, t0);
+        tma_load_3d(st + 16384, &tmK, kb, 64, h, t0);
+        tma_load_3d(st + 24576, &tmQ, kb, 64, h, t0);
+        tma_load_3d(st + SM_V, &tmV, kb, 0, h, t0);
+        tma_load_3d(st + SM_V + 8192, &tmV, kb, 64, h, t0);
     };
-    if (tid == 0) issue_tma(0);
-
-    // total log-decay of a chunk (threads 0..63 each take one row); every thread gets the result
-    auto chunk_log_decay = [&](int c) -> float {
-        float x = 0.f;
-        const int t = t_begin + c * CH + tid;
-        if (tid < 64 && c < nchunks && t < t_end) x = a.lg[(size_t)t * a.H + h];
-        x = warp_sum(x);
-        __syncthreads();
-        if (lane == 0) s_red[warp] = x;
-        __syncthreads();
-        return s_red[0] + s_red[1];
+    // one arrival per warp: every lane has already fenced its own writes, the warp barrier orders them before lane 0's arrive
+    auto warp_arrive = [&](int b) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(b));
+    };
+    // a bounded wait; on failure the whole block is told to leave
+    auto wait = [&](int b, uint32_t parity) -> bool {
+        if (mbar_wait(bar(b), parity, WAIT_LIMIT)) return true;
+        atomicExch(&s_abort, 1);
+        atomicExch(a.status, 3);
+        return false;
     };
 
-    // ---- initial state -> TMEM: unscaled bf16 hi/lo pairs and the fp32 copy pre-scaled by gamma_C of chunk 0 ----
-    float gC_cur = expf(chunk_log_decay(0));
-    for (int blk = 0; blk < 4; blk++) {
-        uint32_t r[32], hi[16], lo[16];
+    if (warp < 4) {
+        // ============================================================================================================
+        // state-independent work: gates, L, A, T = (I + L)^-1, Tb / Tg, and the y epilogue
+        // ============================================================================================================
+        const uint32_t tl = tb + ((uint32_t)(warp * 32) << 16);
+        // barrier among the 128 threads of this group, built on an mbarrier so that it is bounded like every other wait
+        uint32_t grp_phase = 0;
+        auto group_sync = [&]() -> bool {
+            warp_arrive(B_AGRP);
+            const bool okw = wait(B_AGRP, grp_phase);
+            grp_phase ^= 1u;
+            return okw;
+        };
+        // gate inputs are fetched one chunk ahead so that their latency hides behind the previous chunk's work
+        float lg_pre = 0.f, b_pre = 0.f;
+        if (tid < 64 && t_begin + tid < t_end) { lg_pre = a.lg[(size_t)(t_begin + tid) * a.H + h]; b_pre = a.beta[(size_t)(t_begin + tid) * a.H + h]; }
+        for (int c = 0; c < nchunks; c++) {
+            const int stage = c & 1;
+            const uint32_t par = (uint32_t)c & 1u;
+            const int t0 = t_begin + c * CH;
+            const int nrows = min(CH, t_end - t0);
+            if (*(volatile int*)&s_abort) break;
+            // ---- gates: Lc2 = inclusive prefix sum of the log2-decay, gamma, dec, beta ----
+            const float lgj = lg_pre * LOG2E, bj = b_pre;
+            lg_pre = 0.f; b_pre = 0.f;
+            if (tid < 64 && t0 + CH + tid < t_end) { lg_pre = a.lg[(size_t)(t0 + CH + tid) * a.H + h]; b_pre = a.beta[(size_t)(t0 + CH + tid) * a.H + h]; }
+            float xs = lgj;
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-            const float4 v4 = init ? *reinterpret_cast<const float4*>(init + blk * 32 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-            split_pack(v4.x, v4.y, hi[i / 2], lo[i / 2]);
-            split_pack(v4.z, v4.w, hi[i / 2 + 1], lo[i / 2 + 1]);
-            r[i] = __float_as_uint(v4.x * gC_cur); r[i + 1] = __float_as_uint(v4.y * gC_cur);
-            r[i + 2] = __float_as_uint(v4.z * gC_cur); r[i + 3] = __float_as_uint(v4.w * gC_cur);
-        }
-        tmem_st32(tl + TM_S + blk * 32, r);
-        tmem_st16(tl + TM_SHI + blk * 16, hi);
-        tmem_st16(tl + TM_SLO + blk * 16, lo);
-    }
-    tmem_wait_st();
+            for (int o = 1; o < 32; o <<= 1) { const float y = __shfl_up_sync(0xffffffffu, xs, o); if (lane >= o) xs += y; }
+            if (lane == 31 && warp < 2) s_scan[warp] = xs;
+            if (!group_sync()) break;
+            if (warp == 1) xs += s_scan[0];
+            const float Ltot = s_scan[0] + s_scan[1];
+            if (tid < 64) {
+                const float g = ex2(xs);
+                s_Lc[tid] = xs; s_gam[tid] = g; s_ngam[tid] = -g; s_dec[tid] = ex2(Ltot - xs); s_beta[tid] = bj;
+            }
+            if (!wait(stage ? B_KQV1 : B_KQV0, (uint32_t)(c >> 1) & 1u)) break;
+            if (nrows < CH) {
+                // rows past the end of the sequence are zero (qwen35/gdn_nax.py:55-60): 6 tiles x (64 - nrows) rows x 128 B
+                const int nz = (CH - nrows) * 8;
+                for (int i = tid; i < 6 * nz; i += 128) {
+                    const int tile = i / nz, p = i % nz;
+                    *reinterpret_cast<uint4*>(smem + stage * SM_STAGE + tile * 8192 + nrows * 128 + p * 16) = make_uint4(0, 0, 0, 0);
+                }
+                fence_proxy_async_smem();
+            }
+            tc_fence_before_sync();                                  // the previous chunk's reads of the G / AD columns are complete
+            warp_arrive(B_INPUTS);
 
-    constexpr uint32_t I64 = idesc_bf16(128, 64, 0, 0);              // N = 64, both operands K-major
-    constexpr uint32_t I128MN = idesc_bf16(128, 128, 0, 1);          // N = 128, B read MN-major
-    uint32_t mma_phase = 0;
-    bool ok = true;
-
-    for (int c = 0; c < nchunks; c++) {
-        const int stage = c & 1;
-        const uint32_t st = sbase + stage * SM_STAGE;
-        const int t0 = t_begin + c * CH;
-        const int nrows = min(CH, t_end - t0);
-        const bool last = c == nchunks - 1;
-
-        // ---- gates of this chunk: Lc (inclusive prefix sum of the log-decay), gamma, dec, beta; total decay of the next chunk ----
-        float lgj = 0.f, bj = 0.f, lgn = 0.f;
-        if (tid < 64) {
-            if (tid < nrows) { lgj = a.lg[(size_t)(t0 + tid) * a.H + h]; bj = a.beta[(size_t)(t0 + tid) * a.H + h]; }
-            if (!last && t0 + CH + tid < t_end) lgn = a.lg[(size_t)(t0 + CH + tid) * a.H + h];
-        }
-        float xs = lgj;
+            // ---- L (lanes 0..63: fp32 to smem) and A (lanes 64..127: bf16 hi/lo K-major rows) from G = [K;Q] K^T ----
+            if (!wait(B_GDONE, par)) break;
+            tc_fence_after_sync();
+            if (!group_sync()) break;                                // gates are visible to the whole group
+            {
+                const int i = tid & 63;
+                const float Li = s_Lc[i], bi = s_beta[i];
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) { const float y = __shfl_up_sync(0xffffffffu, xs, o); if (lane >= o) xs += y; }
-        const float nsum = warp_sum(lgn);
-        if (lane == 31) s_red[warp] = xs;
-        if (lane == 0) s_red[4 + warp] = nsum;
-        __syncthreads();
-        if (warp == 1) xs += s_red[0];
-        const float Ltot = s_red[0] + s_red[1];
-        const float gC_next = expf(s_red[4] + s_red[5]);
-        if (tid < 64) { s_Lc[tid] = xs; s_gam[tid] = expf(xs); s_dec[tid] = expf(Ltot - xs); s_beta[tid] = bj; }
+                for (int half = 0; half < 2; half++) {
+                    uint32_t r[32];
+                    tmem_ld32(tl + TM_G + half * 32, r);
+                    tmem_wait_ld();
+                    if (tid < 64) {
+#pragma unroll
+                        for (int jj = 0; jj < 32; jj += 4) {
+                            const float4 lc = *reinterpret_cast<const float4*>(s_Lc + half * 32 + jj);
+                            const int j = half * 32 + jj;
+                            // column-major copy Lt[j][i] = L[i][j]: the solve walks down columns
+                            Lm[j * LSTRIDE + i] = (j < i) ? bi * ex2(Li - lc.x) * __uint_as_float(r[jj]) : 0.f;
+                            Lm[(j + 1) * LSTRIDE + i] = (j + 1 < i) ? bi * ex2(Li - lc.y) * __uint_as_float(r[jj + 1]) : 0.f;
+                            Lm[(j + 2) * LSTRIDE + i] = (j + 2 < i) ? bi * ex2(Li - lc.z) * __uint_as_float(r[jj + 2]) : 0.f;
+                            Lm[(j + 3) * LSTRIDE + i] = (j + 3 < i) ? bi * ex2(Li - lc.w) * __uint_as_float(r[jj + 3]) : 0.f;
+                        }
+                    } else {
+#pragma unroll
+                        for (int cb = 0; cb < 4; cb++) {              // 16-byte pieces: 8 columns each
+                            uint32_t hi[4], lo[4];
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const int j = half * 32 + cb * 8 + 2 * e;
+                                const float2 lc = *reinterpret_cast<const float2*>(s_Lc + j);
+                                const float a0 = (j <= i) ? ex2(Li - lc.x) * __uint_as_float(r[cb * 8 + 2 * e]) : 0.f;
+                                const float a1 = (j + 1 <= i) ? ex2(Li - lc.y) * __uint_as_float(r[cb * 8 + 2 * e + 1]) : 0.f;
+                                split_pack(a0, a1, hi[e], lo[e]);
+                            }
+                            const uint32_t o = i * 128 + (((half * 4 + cb) ^ (i & 7)) << 4);
+                            *reinterpret_cast<uint4*>(smem + SM_A_HI + o) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                            *reinterpret_cast<uint4*>(smem + SM_A_LO + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            if (!group_sync()) break;
 
-        // ---- this chunk's tiles have landed; start the next chunk's copy into the other stage ----
-        ok &= mbar_wait(stage ? bar_tma1 : bar_tma0, (uint32_t)(c >> 1) & 1u);
-        if (tid == 0 && !last) issue_tma(c + 1);
-        if (nrows < CH) {
-            // rows past the end of the sequence are zero (qwen35/gdn_nax.py:55-60): 6 tiles x (64 - nrows) rows x 128 B
-            const int nz = (CH - nrows) * 8;                          // 16-byte pieces per tile
-            for (int i = tid; i < 6 * nz; i += 128) {
-                const int tile = i / nz, p = i % nz;
-                *reinterpret_cast<uint4*>(smem + stage * SM_STAGE + tile * 8192 + nrows * 128 + p * 16) = make_uint4(0, 0, 0, 0);
+            // ---- T = (I + L)^-1: one column per thread (threads 0..63), written as fp32 rows ----
+            if (warp == 0) solve_column<0>(Lm, Tm, tid);
+            else if (warp == 1) solve_column<2>(Lm, Tm, tid);
+            if (!group_sync()) break;
+            // ---- Tb = T diag(beta), Tg = -Tb diag(gamma) as bf16 hi/lo K-major rows: thread = (row, half of the columns) ----
+            {
+                const int i = tid >> 1, hf = tid & 1;
+#pragma unroll
+                for (int cb = 0; cb < 4; cb++) {
+                    uint32_t bh[4], bl[4], gh[4], gl[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e += 2) {
+                        const int j = hf * 32 + cb * 8 + 2 * e;
+                        const float4 t4 = *reinterpret_cast<const float4*>(Tm + i * LSTRIDE + j);
+                        const float4 b4 = *reinterpret_cast<const float4*>(s_beta + j);
+                        const float4 g4 = *reinterpret_cast<const float4*>(s_ngam + j);
+                        const float v0 = t4.x * b4.x, v1 = t4.y * b4.y, v2 = t4.z * b4.z, v3 = t4.w * b4.w;
+                        split_pack(v0, v1, bh[e], bl[e]);
+                        split_pack(v2, v3, bh[e + 1], bl[e + 1]);
+                        split_pack(v0 * g4.x, v1 * g4.y, gh[e], gl[e]);
+                        split_pack(v2 * g4.z, v3 * g4.w, gh[e + 1], gl[e + 1]);
+                    }
+                    const uint32_t o = i * 128 + (((hf * 4 + cb) ^ (i & 7)) << 4);
+                    *reinterpret_cast<uint4*>(smem + SM_TB_HI + o) = make_uint4(bh[0], bh[1], bh[2], bh[3]);
+                    *reinterpret_cast<uint4*>(smem + SM_TB_LO + o) = make_uint4(bl[0], bl[1], bl[2], bl[3]);
+                    *reinterpret_cast<uint4*>(smem + SM_TG_HI + o) = make_uint4(gh[0], gh[1], gh[2], gh[3]);
+                    *reinterpret_cast<uint4*>(smem + SM_TG_LO + o) = make_uint4(gl[0], gl[1], gl[2], gl[3]);
+                }
             }
             fence_proxy_async_smem();
-        }
-        tc_fence_before_sync();
-        if (!__syncthreads_and(ok)) break;
+            warp_arrive(B_TB);
 
-        // ---- G = [K; Q] K^T ----
-        if (tid == 0) {
+            // ---- y epilogue: Y^T = P2^T diag(gamma) + A D, transposed through shared memory, 16-byte stores ----
+            if (!wait(B_YDONE, par)) break;
+            tc_fence_after_sync();
+            if (tid == 0 && c + 2 < nchunks) issue_tma(c + 2);       // every reader of this stage (MMAs of chunk c) has finished
+            {
+                __nv_bfloat16* ys = reinterpret_cast<__nv_bfloat16*>(smem + SM_T);       // [64][128]
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    uint32_t p2[32], ad[32];
+                    tmem_ld32(tl + TM_P2 + half * 32, p2);
+                    tmem_ld32(tl + TM_G + half * 32, ad);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int ii = 0; ii < 32; ii++) {
+                        const int i = half * 32 + ii;
+                        ys[i * 128 + tid] = __float2bfloat16_rn(s_gam[i] * __uint_as_float(p2[ii]) + __uint_as_float(ad[ii]));
+                    }
+                }
+                if (!group_sync()) break;
+                __nv_bfloat16* yg = a.y + ((size_t)t0 * a.H + h) * DV;
+#pragma unroll
+                for (int k8 = 0; k8 < 8; k8++) {
+                    const int p = tid + 128 * k8, row = p >> 4, c16 = p & 15;
+                    if (row < nrows)
+                        *reinterpret_cast<uint4*>(yg + (size_t)row * a.H * DV + c16 * 8) = *reinterpret_cast<const uint4*>(ys + row * 128 + c16 * 8);
+                }
+                if (!group_sync()) break;                            // the staging bytes become T of the next chunk
+            }
+        }
+    } else if (warp < 12) {
+        // ============================================================================================================
+        // state-dependent passes between the MMAs: two warps per TMEM lane quadrant, half of the columns each
+        // ============================================================================================================
+        const int cw = warp - 4, q = cw & 3, hf = cw >> 2;
+        const int r = q * 32 + lane;                                 // value row of this thread
+        const uint32_t tl = tb + ((uint32_t)(q * 32) << 16);
+        // this lane's share of the log-decay of chunk c (two rows); summed over the warp it is the chunk's total.  The loads are
+        // issued one chunk before the value is needed.
+        auto decay_part = [&](int c) -> float {
+            float x = 0.f;
+            const int t = t_begin + c * CH + lane;
+            if (c < nchunks) {
+                if (t < t_end) x = a.lg[(size_t)t * a.H + h];
+                if (t + 32 < t_end) x += a.lg[(size_t)(t + 32) * a.H + h];
+            }
+            return x;
+        };
+        float part_next = decay_part(1);
+        // ---- initial state -> TMEM: unscaled bf16 hi/lo pairs and the fp32 copy pre-scaled by gamma_C of chunk 0 ----
+        {
+            const float gC0 = ex2(warp_sum(decay_part(0)) * LOG2E);
+            const float* init = init_head ? init_head + (size_t)r * DK + hf * 64 : nullptr;
+#pragma unroll
+            for (int blk = 0; blk < 2; blk++) {
+                uint32_t rr[32], hi[16], lo[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    const float4 v4 = init ? *reinterpret_cast<const float4*>(init + blk * 32 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    split_pack(v4.x, v4.y, hi[i / 2], lo[i / 2]);
+                    split_pack(v4.z, v4.w, hi[i / 2 + 1], lo[i / 2 + 1]);
+                    rr[i] = __float_as_uint(v4.x * gC0); rr[i + 1] = __float_as_uint(v4.y * gC0);
+                    rr[i + 2] = __float_as_uint(v4.z * gC0); rr[i + 3] = __float_as_uint(v4.w * gC0);
+                }
+                tmem_st32(tl + TM_S + hf * 64 + blk * 32, rr);
+                tmem_st16(tl + TM_SHI + hf * 32 + blk * 16, hi);
+                tmem_st16(tl + TM_SLO + hf * 32 + blk * 16, lo);
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            warp_arrive(B_SREADY);
+        }
+        for (int c = 0; c < nchunks; c++) {
+            const uint32_t par = (uint32_t)c & 1u;
+            const bool last = c == nchunks - 1;
+            if (*(volatile int*)&s_abort) break;
+            const float gC_next = last ? 1.f : ex2(warp_sum(part_next) * LOG2E);
+            part_next = decay_part(c + 2);
+
+            // ---- P1^T -> bf16 hi/lo pairs in TMEM (the A operand of P1^T Tg^T) ----
+            if (!wait(B_P1DONE, par)) break;
+            tc_fence_after_sync();
+            {
+                uint32_t rr[32], hi[16], lo[16];
+                tmem_ld32(tl + TM_P1 + hf * 32, rr);
+                tmem_wait_ld();
+#pragma unroll
+                for (int jj = 0; jj < 32; jj += 2) split_pack(__uint_as_float(rr[jj]), __uint_as_float(rr[jj + 1]), hi[jj / 2], lo[jj / 2]);
+                tmem_st16(tl + TM_ZHI + hf * 16, hi);
+                tmem_st16(tl + TM_ZLO + hf * 16, lo);
+                tmem_wait_st();
+            }
+            tc_fence_before_sync();
+            warp_arrive(B_ZREADY);
+
+            // ---- D^T -> bf16 hi/lo pairs in TMEM (A operand of A D) and Dp^T = D^T diag(dec) -> hi/lo K-major rows in smem ----
+            if (!wait(B_DDONE, par)) break;
+            tc_fence_after_sync();
+            {
+                uint32_t rr[32], hi[16], lo[16];
+                tmem_ld32(tl + TM_P1 + hf * 32, rr);
+                tmem_wait_ld();
+#pragma unroll
+                for (int jj = 0; jj < 32; jj += 2) split_pack(__uint_as_float(rr[jj]), __uint_as_float(rr[jj + 1]), hi[jj / 2], lo[jj / 2]);
+                tmem_st16(tl + TM_ZHI + hf * 16, hi);
+                tmem_st16(tl + TM_ZLO + hf * 16, lo);
+#pragma unroll
+                for (int cb = 0; cb < 4; cb++) {
+                    uint32_t ph[4], pl[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e += 2) {
+                        const int jj = cb * 8 + 2 * e;
+                        const float4 d4 = *reinterpret_cast<const float4*>(s_dec + hf * 32 + jj);
+                        split_pack(__uint_as_float(rr[jj]) * d4.x, __uint_as_float(rr[jj + 1]) * d4.y, ph[e], pl[e]);
+                        split_pack(__uint_as_float(rr[jj + 2]) * d4.z, __uint_as_float(rr[jj + 3]) * d4.w, ph[e + 1], pl[e + 1]);
+                    }
+                    const uint32_t o = r * 128 + (((hf * 4 + cb) ^ (r & 7)) << 4);
+                    *reinterpret_cast<uint4*>(smem + SM_DP_HI + o) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                    *reinterpret_cast<uint4*>(smem + SM_DP_LO + o) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                }
+                tmem_wait_st();
+            }
+            fence_proxy_async_smem();
+            tc_fence_before_sync();
+            warp_arrive(B_DPREADY);
+
+            // ---- new state: bf16 hi/lo pairs for the next chunk's products, fp32 copy pre-scaled by the next gamma_C (or the output) ----
+            if (!wait(B_SDONE, par)) break;
+            tc_fence_after_sync();
+#pragma unroll
+            for (int blk = 0; blk < 2; blk++) {
+                uint32_t rr[32], hi[16], lo[16];
+                tmem_ld32(tl + TM_S + hf * 64 + blk * 32, rr);
+                tmem_wait_ld();
+                if (last) {
+                    float* fin = fin_head + (size_t)r * DK + hf * 64 + blk * 32;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(fin + i) = make_float4(__uint_as_float(rr[i]), __uint_as_float(rr[i + 1]), __uint_as_float(rr[i + 2]),
+                                                                         __uint_as_float(rr[i + 3]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) split_pack(__uint_as_float(rr[i]), __uint_as_float(rr[i + 1]), hi[i / 2], lo[i / 2]);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * gC_next);
+                    tmem_st16(tl + TM_SHI + hf * 32 + blk * 16, hi);
+                    tmem_st16(tl + TM_SLO + hf * 32 + blk * 16, lo);
+                    tmem_st32(tl + TM_S + hf * 64 + blk * 32, rr);
+                }
+            }
+            if (!last) {
+                tmem_wait_st();
+                tc_fence_before_sync();
+                warp_arrive(B_SREADY);
+            }
+        }
+    } else if (lane == 0) {
+        // ============================================================================================================
+        // the MMA issuer (one thread)
+        // ============================================================================================================
+        constexpr uint32_t I64 = idesc_bf16(128, 64, 0, 0);          // N = 64, A and B K-major (A may also come from TMEM)
+        constexpr uint32_t I64_AMN = idesc_bf16(128, 64, 1, 0);      // N = 64, A read MN-major (V as V^T)
+        constexpr uint32_t I128_BMN = idesc_bf16(128, 128, 0, 1);    // N = 128, B read MN-major (K as the [tokens x dk] factor)
+        issue_tma(0);
+        if (nchunks > 1) issue_tma(1);
+        for (int c = 0; c < nchunks; c++) {
+            const uint32_t par = (uint32_t)c & 1u;
+            const uint32_t st = sbase + (c & 1) * SM_STAGE;
+            if (*(volatile int*)&s_abort) break;
+            // ---- G = [K; Q] K^T ----
+            if (!wait(B_INPUTS, par)) break;
             tc_fence_after_sync();
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) {
                 const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-                mma_ss(tb + TM_G, smem_desc_sw128(st + off, 16, 1024), smem_desc_sw128(st + off, 16, 1024), I64, ks > 0);
+                const uint64_t d = smem_desc_sw128(st + off, 16, 1024);
+                mma_ss(tb + TM_G, d, d, I64, ks > 0);
             }
-            mma_commit(bar_mma);
-        }
-        ok &= mbar_wait(bar_mma, mma_phase); mma_phase ^= 1;
-        tc_fence_after_sync();
-
-        // ---- L (threads 0..63, fp32 to smem) and A (threads 64..127, bf16 hi/lo K-major rows) from G ----
-        {
-            const int i = tid & 63;
-            const float Li = s_Lc[i], bi = s_beta[i];
-#pragma unroll
-            for (int half = 0; half < 2; half++) {
-                uint32_t r[32];
-                tmem_ld32(tl + TM_G + half * 32, r);
-                tmem_wait_ld();
-                if (tid < 64) {
-#pragma unroll
-                    for (int jj = 0; jj < 32; jj += 4) {
-                        float4 o;
-                        float* op = &o.x;
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const int j = half * 32 + jj + e;
-                            op[e] = (j < i) ? bi * expf(Li - s_Lc[j]) * __uint_as_float(r[jj + e]) : 0.f;
-                        }
-                        *reinterpret_cast<float4*>(Lm + i * LSTRIDE + half * 32 + jj) = o;
-                    }
-                } else {
-#pragma unroll
-                    for (int cb = 0; cb < 4; cb++) {                  // 16-byte pieces: 8 columns each
-                        uint32_t hi[4], lo[4];
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            const int j = half * 32 + cb * 8 + 2 * e;
-                            const float a0 = (j <= i) ? expf(Li - s_Lc[j]) * __uint_as_float(r[cb * 8 + 2 * e]) : 0.f;
-                            const float a1 = (j + 1 <= i) ? expf(Li - s_Lc[j + 1]) * __uint_as_float(r[cb * 8 + 2 * e + 1]) : 0.f;
-                            split_pack(a0, a1, hi[e], lo[e]);
-                        }
-                        const uint32_t o = i * 128 + (((half * 4 + cb) ^ (i & 7)) << 4);
-                        *reinterpret_cast<uint4*>(smem + SM_A_HI + o) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                        *reinterpret_cast<uint4*>(smem + SM_A_LO + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                    }
-                }
-            }
-        }
-        __syncthreads();
-
-        // ---- T = (I + L)^-1 by forward substitution, one column per thread; Tb = T diag(beta) as bf16 hi/lo, K-major rows ----
-        if (tid < 64) {
-            float x[64];
-            if (warp == 0) solve_column<0>(Lm, tid, x); else solve_column<32>(Lm, tid, x);
-            const float bj2 = s_beta[tid];
-            const uint32_t cpiece = (uint32_t)(tid >> 3), cin = (uint32_t)(tid & 7) * 2;
-#pragma unroll
-            for (int i = 0; i < 64; i++) {
-                const float tv = x[i] * bj2;
-                const float hi = bf(tv);
-                const uint32_t o = i * 128 + ((cpiece ^ (i & 7)) << 4) + cin;
-                *reinterpret_cast<__nv_bfloat16*>(smem + SM_TB_HI + o) = __float2bfloat16_rn(hi);
-                *reinterpret_cast<__nv_bfloat16*>(smem + SM_TB_LO + o) = __float2bfloat16_rn(tv - hi);
-            }
-        }
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        __syncthreads();
-
-        // ---- P1^T = S0 K^T, P2^T = S0 Q^T (S0 = hi + lo from TMEM) ----
-        if (tid == 0) {
+            mma_commit(bar(B_GDONE));
+            // ---- P1^T = S0 K^T, P2^T = S0 Q^T (S0 = hi + lo from TMEM) ----
+            if (!wait(B_SREADY, par)) break;
             tc_fence_after_sync();
 #pragma unroll
             for (int part = 0; part < 2; part++) {
@@ -303,7 +505,7 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     mma_ts(tb + TM_P1, tb + acol + ks * 8, smem_desc_sw128(st + off, 16, 1024), I64, (part | ks) != 0);
                 }
             }
-            mma_commit(bar_mma);
+            mma_commit(bar(B_P1DONE));
 #pragma unroll
             for (int part = 0; part < 2; part++) {
                 const uint32_t acol = part ? TM_SLO : TM_SHI;
@@ -313,86 +515,37 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     mma_ts(tb + TM_P2, tb + acol + ks * 8, smem_desc_sw128(st + off, 16, 1024), I64, (part | ks) != 0);
                 }
             }
-        }
-        ok &= mbar_wait(bar_mma, mma_phase); mma_phase ^= 1;
-        tc_fence_after_sync();
-
-        // ---- Z^T = V^T - P1^T diag(gamma) -> bf16 hi/lo pairs in TMEM ----
-        {
-            const unsigned char* vt = smem + stage * SM_STAGE + SM_V + (tid >> 6) * 8192;
-            const int vc = tid & 63;
-            const uint32_t vpiece = (uint32_t)(vc >> 3), vin = (uint32_t)(vc & 7) * 2;
-#pragma unroll
-            for (int half = 0; half < 2; half++) {
-                uint32_t r[32], hi[16], lo[16];
-                tmem_ld32(tl + TM_P1 + half * 32, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int jj = 0; jj < 32; jj += 2) {
-                    const int j = half * 32 + jj;
-                    const float v0 = ldbf(reinterpret_cast<const __nv_bfloat16*>(vt + j * 128 + ((vpiece ^ (j & 7)) << 4) + vin));
-                    const float v1 = ldbf(reinterpret_cast<const __nv_bfloat16*>(vt + (j + 1) * 128 + ((vpiece ^ ((j + 1) & 7)) << 4) + vin));
-                    const float z0 = v0 - s_gam[j] * __uint_as_float(r[jj]);
-                    const float z1 = v1 - s_gam[j + 1] * __uint_as_float(r[jj + 1]);
-                    split_pack(z0, z1, hi[jj / 2], lo[jj / 2]);
-                }
-                tmem_st16(tl + TM_ZHI + half * 16, hi);
-                tmem_st16(tl + TM_ZLO + half * 16, lo);
-            }
-            tmem_wait_st();
-        }
-        tc_fence_before_sync();
-        if (!__syncthreads_and(ok)) break;
-
-        // ---- D^T = Z^T Tb^T  (hi*hi + lo*hi + hi*lo) ----
-        if (tid == 0) {
+            // ---- D^T = V^T Tb^T + P1^T Tg^T (the P1 columns become the D accumulator once P1 has been split) ----
+            if (!wait(B_TB, par)) break;
+            if (!wait(B_ZREADY, par)) break;
             tc_fence_after_sync();
+#pragma unroll
+            for (int part = 0; part < 2; part++) {
+                const uint32_t bsm = sbase + (part ? SM_TB_LO : SM_TB_HI);
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++)
+                    mma_ss(tb + TM_P1, smem_desc_sw128(st + SM_V + ks * 2048, 8192, 1024), smem_desc_sw128(bsm + ks * 32, 16, 1024), I64_AMN,
+                           (part | ks) != 0);
+            }
 #pragma unroll
             for (int term = 0; term < 3; term++) {
                 const uint32_t acol = term == 1 ? TM_ZLO : TM_ZHI;
-                const uint32_t bsm = sbase + (term == 2 ? SM_TB_LO : SM_TB_HI);
+                const uint32_t bsm = sbase + (term == 2 ? SM_TG_LO : SM_TG_HI);
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++) mma_ts(tb + TM_P1, tb + acol + ks * 8, smem_desc_sw128(bsm + ks * 32, 16, 1024), I64, 1);
+            }
+            mma_commit(bar(B_DDONE));
+            // ---- state update S += Dp^T K, then A D into the G columns ----
+            if (!wait(B_DPREADY, par)) break;
+            tc_fence_after_sync();
+#pragma unroll
+            for (int part = 0; part < 2; part++) {
+                const uint32_t asm_ = sbase + (part ? SM_DP_LO : SM_DP_HI);
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++)
-                    mma_ts(tb + TM_P1, tb + acol + ks * 8, smem_desc_sw128(bsm + ks * 32, 16, 1024), I64, (term | ks) != 0);
+                    mma_ss(tb + TM_S, smem_desc_sw128(asm_ + ks * 32, 16, 1024), smem_desc_sw128(st + ks * 2048, 16384, 1024), I128_BMN, 1);
             }
-            mma_commit(bar_mma);
-        }
-        ok &= mbar_wait(bar_mma, mma_phase); mma_phase ^= 1;
-        tc_fence_after_sync();
-
-        // ---- D^T -> bf16 hi/lo pairs in TMEM (A operand of A D) and Dp^T = D^T diag(dec) -> hi/lo K-major rows in smem ----
-        {
-#pragma unroll
-            for (int half = 0; half < 2; half++) {
-                uint32_t r[32], hi[16], lo[16];
-                tmem_ld32(tl + TM_P1 + half * 32, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int jj = 0; jj < 32; jj += 2) split_pack(__uint_as_float(r[jj]), __uint_as_float(r[jj + 1]), hi[jj / 2], lo[jj / 2]);
-                tmem_st16(tl + TM_ZHI + half * 16, hi);
-                tmem_st16(tl + TM_ZLO + half * 16, lo);
-#pragma unroll
-                for (int cb = 0; cb < 4; cb++) {
-                    uint32_t ph[4], pl[4];
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const int jj = cb * 8 + 2 * e, j = half * 32 + jj;
-                        split_pack(__uint_as_float(r[jj]) * s_dec[j], __uint_as_float(r[jj + 1]) * s_dec[j + 1], ph[e], pl[e]);
-                    }
-                    const uint32_t o = tid * 128 + (((half * 4 + cb) ^ (tid & 7)) << 4);
-                    *reinterpret_cast<uint4*>(smem + SM_DP_HI + o) = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                    *reinterpret_cast<uint4*>(smem + SM_DP_LO + o) = make_uint4(pl[0], pl[1], pl[2], pl[3]);
-                }
-            }
-            tmem_wait_st();
-        }
-        fence_proxy_async_smem();
-        tc_fence_before_sync();
-        if (!__syncthreads_and(ok)) break;
-
-        // ---- A D (into the G columns) and the state update S += Dp^T K ----
-        if (tid == 0) {
-            tc_fence_after_sync();
+            mma_commit(bar(B_SDONE));
 #pragma unroll
             for (int term = 0; term < 3; term++) {
                 const uint32_t acol = term == 1 ? TM_ZLO : TM_ZHI;
@@ -401,60 +554,9 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 for (int ks = 0; ks < 4; ks++)
                     mma_ts(tb + TM_G, tb + acol + ks * 8, smem_desc_sw128(bsm + ks * 32, 16, 1024), I64, (term | ks) != 0);
             }
-#pragma unroll
-            for (int part = 0; part < 2; part++) {
-                const uint32_t asm_ = sbase + (part ? SM_DP_LO : SM_DP_HI);
-#pragma unroll
-                for (int ks = 0; ks < 4; ks++)
-                    mma_ss(tb + TM_S, smem_desc_sw128(asm_ + ks * 32, 16, 1024), smem_desc_sw128(st + ks * 2048, 16384, 1024), I128MN, 1);
-            }
-            mma_commit(bar_mma);
+            mma_commit(bar(B_YDONE));
         }
-        ok &= mbar_wait(bar_mma, mma_phase); mma_phase ^= 1;
-        tc_fence_after_sync();
-
-        // ---- Y^T = P2^T diag(gamma) + A D  ->  y[t0 + i, h, v]  (thread v = value row) ----
-        {
-            __nv_bfloat16* yp = a.y + ((size_t)t0 * a.H + h) * DV + tid;
-#pragma unroll
-            for (int half = 0; half < 2; half++) {
-                uint32_t p2[32], ad[32];
-                tmem_ld32(tl + TM_P2 + half * 32, p2);
-                tmem_ld32(tl + TM_G + half * 32, ad);
-                tmem_wait_ld();
-#pragma unroll
-                for (int ii = 0; ii < 32; ii++) {
-                    const int i = half * 32 + ii;
-                    if (i < nrows) yp[(size_t)i * a.H * DV] = __float2bfloat16_rn(s_gam[i] * __uint_as_float(p2[ii]) + __uint_as_float(ad[ii]));
-                }
-            }
-        }
-        // ---- new state: bf16 hi/lo pairs for the next chunk's products, fp32 copy pre-scaled by the next gamma_C (or the output) ----
-        for (int blk = 0; blk < 4; blk++) {
-            uint32_t r[32], hi[16], lo[16];
-            tmem_ld32(tl + TM_S + blk * 32, r);
-            tmem_wait_ld();
-            if (last) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 4)
-                    *reinterpret_cast<float4*>(fin + blk * 32 + i) = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
-                                                                               __uint_as_float(r[i + 3]));
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) split_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), hi[i / 2], lo[i / 2]);
-#pragma unroll
-                for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * gC_next);
-                tmem_st16(tl + TM_SHI + blk * 16, hi);
-                tmem_st16(tl + TM_SLO + blk * 16, lo);
-                tmem_st32(tl + TM_S + blk * 32, r);
-            }
-        }
-        tmem_wait_st();
-        gC_cur = gC_next;
-        tc_fence_before_sync();
-        if (!__syncthreads_and(ok)) break;
     }
-    if (!ok && tid == 0) atomicExch(a.status, 3);                    // a bounded wait gave up
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tb, 512);
@@ -507,7 +609,7 @@ int launch_prefill(const void* q, const void* k, const void* v, const PrefillArg
             return check_launch("gdn_prefill smem attribute");
         attr_set[dev] = true;
     }
-    gdn_prefill_kernel<<<a.n_seq * a.n_heads, 128, smem, stream>>>(tq, tk, tv, a);
+    gdn_prefill_kernel<<<a.n_seq * a.n_heads, PF_THREADS, smem, stream>>>(tq, tk, tv, a);
     return check_launch("gdn_prefill");
 }
 
