@@ -23,11 +23,15 @@
 // Q and V are bf16 already.  (I + L)^-1 is an exact fp32 forward substitution (one column per thread), as in the reference
 // (qwen35/gdn_nax.py:118-141); the tensor-core products with T are the "solve products".
 //
-// Roles (416 threads): warps 0-3 build everything that does not depend on the state (gates, L, A, the solve, Tb / Tg) and write
-// y; warps 4-11 do the state-dependent passes between MMAs (two warps per TMEM lane quadrant, half of the columns each); lane 0
-// of warp 12 issues every tcgen05.mma.  The groups hand over through mbarriers; K/Q/V chunks arrive by TMA (128-byte swizzle,
-// no multicast), double buffered; rows of a partial last chunk are zeroed in shared memory so that a packed neighbour
-// sequence can never leak in.  Every wait is bounded: a wait that gives up sets the device status word and the block leaves.
+// Roles (544 threads, one block per SM):
+//   warps 0-3   "solver": everything that does not depend on the state, one chunk ahead of the chain: gates, L from K K^T,
+//               the forward substitution, Tb / Tg
+//   warps 4-11  "chain": the state-dependent passes between MMAs (two warps per TMEM lane quadrant, half of the columns each)
+//   warp 12     lane 0 issues every tcgen05.mma
+//   warps 13-16 "output": the A matrix from Q K^T, the y rows, and the TMA loads of the chunk after next
+// The groups hand over through mbarriers (one arrival per warp); K/Q/V chunks arrive by TMA (128-byte swizzle, no multicast),
+// double buffered; rows of a partial last chunk are zeroed in shared memory so that a packed neighbour sequence can never leak
+// in.  Every wait is bounded: a wait that gives up sets the device status word and the block leaves.
 #include <cuda.h>
 #include "gdn_common.cuh"
 #include "launchers.cuh"
@@ -38,7 +42,7 @@ namespace gdn {
 using namespace sm100;
 
 constexpr int CH = 64;                               // chunk length
-constexpr int PF_THREADS = 416;
+constexpr int PF_THREADS = 544;
 // ---- shared memory map (bytes from a 1024-aligned base) ----
 constexpr int SM_STAGE = 48 * 1024;                  // per stage: [K_h0 | Q_h0 | K_h1 | Q_h1] (4 x 8 KiB) + [V_h0 | V_h1] (2 x 8 KiB)
 constexpr int SM_V = 32 * 1024;                      // offset of V inside a stage
@@ -52,21 +56,23 @@ constexpr int SM_DP_HI = SM_A_LO + 8192;             // Dp^T hi / lo: [128][64] 
 constexpr int SM_DP_LO = SM_DP_HI + 16384;
 constexpr int SM_L = SM_DP_LO + 16384;               // L fp32, column-major: Lt[j][i] = L[i][j], [64][LSTRIDE]
 constexpr int LSTRIDE = 68;
-constexpr int SM_T = SM_L + 64 * LSTRIDE * 4;        // T fp32 [64][LSTRIDE]; the same bytes stage y [64][128] bf16 for the epilogue
-constexpr int SM_GATES = SM_T + 64 * LSTRIDE * 4;    // Lc2, gamma, -gamma, dec, beta: [64] fp32 each
-constexpr int SM_TOTAL = SM_GATES + 5 * 256 + 64;
+constexpr int SM_T = SM_L + 64 * LSTRIDE * 4;        // T fp32 [64][LSTRIDE]
+constexpr int SM_GATES = SM_T + 64 * LSTRIDE * 4;    // three sets (chunk mod 3) of Lc2, gamma, -gamma, dec, beta: [64] fp32 each
+constexpr int GATE_SET = 5 * 64;                     // floats per set
+constexpr int SM_TOTAL = SM_GATES + 3 * GATE_SET * 4 + 64;
 // ---- tensor memory map (columns) ----
 constexpr uint32_t TM_S = 0;                         // fp32 state, pre-scaled by the coming chunk's gamma_C   [128 cols]
 constexpr uint32_t TM_SHI = 128, TM_SLO = 192;       // bf16 pairs of the unscaled state                        [64 + 64]
-constexpr uint32_t TM_G = 256;                       // [K;Q] K^T, later A D                                    [64]
+constexpr uint32_t TM_G = 256;                       // [K;Q] K^T                                               [64]
 constexpr uint32_t TM_P1 = 320;                      // S0 K^T, later D^T                                       [64]
-constexpr uint32_t TM_P2 = 384;                      // S0 Q^T                                                  [64]
+constexpr uint32_t TM_Y = 384;                       // S0 Q^T, scaled by gamma, then + A D = Y^T               [64]
 constexpr uint32_t TM_ZHI = 448, TM_ZLO = 480;       // P1^T, later D^T, as bf16 pairs                          [32 + 32]
 // ---- mbarriers ----
-enum { B_KQV0 = 0, B_KQV1, B_INPUTS, B_GDONE, B_TB, B_SREADY, B_P1DONE, B_ZREADY, B_DDONE, B_DPREADY, B_SDONE, B_YDONE, B_AGRP, B_COUNT };
+enum { B_KQV0 = 0, B_KQV1, B_INPUTS, B_GFREE, B_GDONE, B_TB, B_AREADY, B_YFREE, B_SREADY, B_P1DONE, B_ZREADY, B_DDONE, B_DPREADY, B_SDONE,
+       B_YSCALED, B_YDONE, B_AGRP, B_COUNT };
 
 constexpr float LOG2E = 1.4426950408889634f;
-constexpr uint32_t WAIT_LIMIT = 2000000u;
+constexpr uint32_t WAIT_LIMIT = 200000u;               // polls of up to ~20 us each
 
 __device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 
@@ -75,46 +81,75 @@ __device__ __forceinline__ void split_pack(float x0, float x1, uint32_t& hi, uin
     lo = pack_bf16x2(x0 - __uint_as_float(hi << 16), x1 - __uint_as_float(hi & 0xffff0000u));
 }
 
-// Exact forward substitution for column j of T = (I + L)^-1 (x_i = [i == j] - sum_{m < i} L[i][m] x_m), 16 rows at a time:
-// the contribution of all earlier rows is a rolled loop (x_m is read back from this thread's own column of Tm, L comes as the
-// column-major copy Lt[m][i] so that 16 rows of one column are four broadcast float4 loads), the 16 x 16 triangle inside the
-// block is unrolled.  Sixteen independent accumulators keep the FMA pipe busy and the code stays small enough for the
-// instruction cache (a fully unrolled 64 x 64 substitution does not).  B0 = first block with a non-zero row for this warp.
-template <int B0>
-__device__ __forceinline__ void solve_column(const float* Lt, float* Tm, int j) {
-#pragma unroll
-    for (int i = 0; i < 16 * B0; i++) Tm[i * LSTRIDE + j] = 0.f;
-#pragma unroll
-    for (int b = B0; b < 4; b++) {
+// Exact forward substitution for column j of T = (I + L)^-1 (x_i = [i == j] - sum_{m < i} L[i][m] x_m), 16 rows at a time, two
+// threads per column.  The contribution of all earlier rows is a rolled loop that the two threads of a column split by the
+// parity of m (x_m is read back from the column's own entries of Tm; L comes as the column-major copy Lt[m][i], so 16 rows of
+// one column are four broadcast float4 loads); the 16 x 16 triangle inside the block is unrolled and done by both threads.
+// Sixteen independent accumulators keep the FMA pipe busy.  The block loop is deliberately NOT unrolled and nothing is
+// specialised per warp: the whole routine is ~400 instructions that every block and every warp re-executes, whereas a fully
+// unrolled 64 x 64 substitution (or one copy per warp) streams tens of KiB of straight-line code through the instruction cache
+// for every chunk and runs several times slower.  b0 = first 16-row block that can be non-zero for the columns of this warp.
+__device__ __forceinline__ void solve_column(const float* __restrict__ Lt, float* __restrict__ Tm, int j, int p, int b0) {
+    if (p == 0)
+        for (int i = 0; i < 16 * b0; i++) Tm[i * LSTRIDE + j] = 0.f;
+#pragma unroll 1
+    for (int b = b0; b < 4; b++) {
         float acc[16];
 #pragma unroll
-        for (int ii = 0; ii < 16; ii++) acc[ii] = (16 * b + ii == j) ? 1.f : 0.f;
-#pragma unroll 2
-        for (int m = 16 * B0; m < 16 * b; m++) {
-            const float xm = Tm[m * LSTRIDE + j];
-            const float4* lp = reinterpret_cast<const float4*>(Lt + m * LSTRIDE + 16 * b);
+        for (int ii = 0; ii < 16; ii++) acc[ii] = (p == 0 && 16 * b + ii == j) ? 1.f : 0.f;
+        if (b > b0) {
+#pragma unroll 4
+            for (int m = 16 * b0 + p; m < 16 * b; m += 2) {
+                const float xm = Tm[m * LSTRIDE + j];
+                const float4* lp = reinterpret_cast<const float4*>(Lt + m * LSTRIDE + 16 * b);
 #pragma unroll
-            for (int v4 = 0; v4 < 4; v4++) {
-                const float4 l = lp[v4];
-                acc[4 * v4] -= l.x * xm; acc[4 * v4 + 1] -= l.y * xm; acc[4 * v4 + 2] -= l.z * xm; acc[4 * v4 + 3] -= l.w * xm;
+                for (int v4 = 0; v4 < 4; v4++) {
+                    const float4 l = lp[v4];
+                    acc[4 * v4] -= l.x * xm; acc[4 * v4 + 1] -= l.y * xm; acc[4 * v4 + 2] -= l.z * xm; acc[4 * v4 + 3] -= l.w * xm;
+                }
             }
+#pragma unroll
+            for (int ii = 0; ii < 16; ii++) acc[ii] += __shfl_xor_sync(0xffffffffu, acc[ii], 1);
         }
+        const float* lblk = Lt + (16 * b) * LSTRIDE + 16 * b;        // Lt[16b + ii][16b + kk] = L[16b + kk][16b + ii]
+        float* tcol = Tm + (16 * b) * LSTRIDE + j;
+        // right-looking elimination inside the block; the column of step ii + 1 is fetched before the FMAs of step ii, so the
+        // loop-carried dependence is a single FMA per step (no store inside the loop: stores would pin the loads in place)
+        float4 cur[4], nxt[4];
+#pragma unroll
+        for (int v4 = 0; v4 < 4; v4++) cur[v4] = *reinterpret_cast<const float4*>(lblk + 4 * v4);
 #pragma unroll
         for (int ii = 0; ii < 16; ii++) {
-            const float x = acc[ii];
-            Tm[(16 * b + ii) * LSTRIDE + j] = x;
-            const float* lrow = Lt + (16 * b + ii) * LSTRIDE + 16 * b;
+            if (ii + 1 < 16) {
 #pragma unroll
-            for (int kk = ii + 1; kk < 16; kk++) acc[kk] -= lrow[kk] * x;
+                for (int v4 = (ii + 2) / 4; v4 < 4; v4++) nxt[v4] = *reinterpret_cast<const float4*>(lblk + (ii + 1) * LSTRIDE + 4 * v4);
+            }
+            const float x = acc[ii];
+#pragma unroll
+            for (int v4 = (ii + 1) / 4; v4 < 4; v4++) {
+                const float4 l = cur[v4];
+                if (4 * v4 > ii) acc[4 * v4] -= l.x * x;
+                if (4 * v4 + 1 > ii) acc[4 * v4 + 1] -= l.y * x;
+                if (4 * v4 + 2 > ii) acc[4 * v4 + 2] -= l.z * x;
+                if (4 * v4 + 3 > ii) acc[4 * v4 + 3] -= l.w * x;
+            }
+#pragma unroll
+            for (int v4 = 0; v4 < 4; v4++) cur[v4] = nxt[v4];
         }
+        if (p == 0) {
+#pragma unroll
+            for (int ii = 0; ii < 16; ii++) tcol[ii * LSTRIDE] = acc[ii];
+        }
+        __syncwarp();
     }
 }
 
 __global__ void __launch_bounds__(PF_THREADS, 1)
 gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const PrefillArgs a) {
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // the swizzled tiles need a 1024-byte aligned base; the declared alignment provides it (checked below).  The array is used
+    // directly, not through a re-aligned pointer, so that the compiler keeps every access in the shared address space
+    extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint64_t bars[B_COUNT];
     __shared__ uint32_t tmem_slot;
     __shared__ float s_scan[4];
@@ -139,19 +174,25 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int nchunks = (len + CH - 1) / CH;
 
     const uint32_t sbase = smem_addr(smem);
+    if (sbase & 1023u) { if (tid == 0) atomicExch(a.status, 4); return; }
     auto bar = [&](int i) -> uint32_t { return smem_addr(&bars[i]); };
     float* Lm = reinterpret_cast<float*>(smem + SM_L);
     float* Tm = reinterpret_cast<float*>(smem + SM_T);
-    float* s_Lc = reinterpret_cast<float*>(smem + SM_GATES);          // cumulative log2-decay
-    float* s_gam = s_Lc + 64;
-    float* s_ngam = s_gam + 64;
-    float* s_dec = s_ngam + 64;
-    float* s_beta = s_dec + 64;
+    float* gates_base = reinterpret_cast<float*>(smem + SM_GATES);
+    // gate arrays of chunk c: Lc2 (cumulative log2-decay), gamma, -gamma, dec, beta.  Three sets: the solver writes set c while
+    // the chain may still read set c-1 and c-2 is certainly retired (the solver has seen the D MMAs of chunk c-2 complete, and
+    // those were issued after every reader of set c-3 had finished)
+    auto g_Lc = [&](int c) -> float* { return gates_base + (c % 3) * GATE_SET; };
+    auto g_gam = [&](int c) -> float* { return gates_base + (c % 3) * GATE_SET + 64; };
+    auto g_ngam = [&](int c) -> float* { return gates_base + (c % 3) * GATE_SET + 128; };
+    auto g_dec = [&](int c) -> float* { return gates_base + (c % 3) * GATE_SET + 192; };
+    auto g_beta = [&](int c) -> float* { return gates_base + (c % 3) * GATE_SET + 256; };
 
     if (tid == 0) {
         mbar_init(bar(B_KQV0), 1); mbar_init(bar(B_KQV1), 1);
         mbar_init(bar(B_INPUTS), 4); mbar_init(bar(B_TB), 4); mbar_init(bar(B_AGRP), 4);
-        mbar_init(bar(B_SREADY), 8); mbar_init(bar(B_ZREADY), 8); mbar_init(bar(B_DPREADY), 8);
+        mbar_init(bar(B_GFREE), 2); mbar_init(bar(B_AREADY), 2); mbar_init(bar(B_YFREE), 4);
+        mbar_init(bar(B_SREADY), 8); mbar_init(bar(B_ZREADY), 8); mbar_init(bar(B_DPREADY), 8); mbar_init(bar(B_YSCALED), 8);
         mbar_init(bar(B_GDONE), 1); mbar_init(bar(B_P1DONE), 1); mbar_init(bar(B_DDONE), 1); mbar_init(bar(B_SDONE), 1); mbar_init(bar(B_YDONE), 1);
         s_abort = 0;
         fence_barrier_init();
@@ -182,20 +223,20 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     };
     // a bounded wait; on failure the whole block is told to leave
     auto wait = [&](int b, uint32_t parity) -> bool {
-        if (mbar_wait(bar(b), parity, WAIT_LIMIT)) return true;
+        if (mbar_wait(bar(b), parity & 1u, WAIT_LIMIT)) return true;
         atomicExch(&s_abort, 1);
         atomicExch(a.status, 3);
         return false;
     };
+    auto aborted = [&]() -> bool { return *(volatile int*)&s_abort != 0; };
 
     if (warp < 4) {
         // ============================================================================================================
-        // state-independent work: gates, L, A, T = (I + L)^-1, Tb / Tg, and the y epilogue
+        // solver: gates, L, T = (I + L)^-1, Tb / Tg -- runs up to one chunk ahead of the chain
         // ============================================================================================================
         const uint32_t tl = tb + ((uint32_t)(warp * 32) << 16);
-        // barrier among the 128 threads of this group, built on an mbarrier so that it is bounded like every other wait
         uint32_t grp_phase = 0;
-        auto group_sync = [&]() -> bool {
+        auto group_sync = [&]() -> bool {                            // barrier among the 4 warps, bounded like every other wait
             warp_arrive(B_AGRP);
             const bool okw = wait(B_AGRP, grp_phase);
             grp_phase ^= 1u;
@@ -206,10 +247,9 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (tid < 64 && t_begin + tid < t_end) { lg_pre = a.lg[(size_t)(t_begin + tid) * a.H + h]; b_pre = a.beta[(size_t)(t_begin + tid) * a.H + h]; }
         for (int c = 0; c < nchunks; c++) {
             const int stage = c & 1;
-            const uint32_t par = (uint32_t)c & 1u;
             const int t0 = t_begin + c * CH;
             const int nrows = min(CH, t_end - t0);
-            if (*(volatile int*)&s_abort) break;
+            if (aborted()) break;
             // ---- gates: Lc2 = inclusive prefix sum of the log2-decay, gamma, dec, beta ----
             const float lgj = lg_pre * LOG2E, bj = b_pre;
             lg_pre = 0.f; b_pre = 0.f;
@@ -223,9 +263,9 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const float Ltot = s_scan[0] + s_scan[1];
             if (tid < 64) {
                 const float g = ex2(xs);
-                s_Lc[tid] = xs; s_gam[tid] = g; s_ngam[tid] = -g; s_dec[tid] = ex2(Ltot - xs); s_beta[tid] = bj;
+                g_Lc(c)[tid] = xs; g_gam(c)[tid] = g; g_ngam(c)[tid] = -g; g_dec(c)[tid] = ex2(Ltot - xs); g_beta(c)[tid] = bj;
             }
-            if (!wait(stage ? B_KQV1 : B_KQV0, (uint32_t)(c >> 1) & 1u)) break;
+            if (!wait(stage ? B_KQV1 : B_KQV0, (uint32_t)(c >> 1))) break;
             if (nrows < CH) {
                 // rows past the end of the sequence are zero (qwen35/gdn_nax.py:55-60): 6 tiles x (64 - nrows) rows x 128 B
                 const int nz = (CH - nrows) * 8;
@@ -235,61 +275,45 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 }
                 fence_proxy_async_smem();
             }
-            tc_fence_before_sync();                                  // the previous chunk's reads of the G / AD columns are complete
+            tc_fence_before_sync();                                  // this group's reads of the previous G are complete
             warp_arrive(B_INPUTS);
 
-            // ---- L (lanes 0..63: fp32 to smem) and A (lanes 64..127: bf16 hi/lo K-major rows) from G = [K;Q] K^T ----
-            if (!wait(B_GDONE, par)) break;
+            // ---- L from G = [K;Q] K^T (lanes 0..63), stored column-major in fp32 ----
+            if (!wait(B_GDONE, (uint32_t)c)) break;
             tc_fence_after_sync();
             if (!group_sync()) break;                                // gates are visible to the whole group
-            {
-                const int i = tid & 63;
-                const float Li = s_Lc[i], bi = s_beta[i];
+            if (tid < 64) {
+                const int i = tid;
+                const float* Lc = g_Lc(c);
+                const float Li = Lc[i], bi = g_beta(c)[i];
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
                     uint32_t r[32];
                     tmem_ld32(tl + TM_G + half * 32, r);
                     tmem_wait_ld();
-                    if (tid < 64) {
 #pragma unroll
-                        for (int jj = 0; jj < 32; jj += 4) {
-                            const float4 lc = *reinterpret_cast<const float4*>(s_Lc + half * 32 + jj);
-                            const int j = half * 32 + jj;
-                            // column-major copy Lt[j][i] = L[i][j]: the solve walks down columns
-                            Lm[j * LSTRIDE + i] = (j < i) ? bi * ex2(Li - lc.x) * __uint_as_float(r[jj]) : 0.f;
-                            Lm[(j + 1) * LSTRIDE + i] = (j + 1 < i) ? bi * ex2(Li - lc.y) * __uint_as_float(r[jj + 1]) : 0.f;
-                            Lm[(j + 2) * LSTRIDE + i] = (j + 2 < i) ? bi * ex2(Li - lc.z) * __uint_as_float(r[jj + 2]) : 0.f;
-                            Lm[(j + 3) * LSTRIDE + i] = (j + 3 < i) ? bi * ex2(Li - lc.w) * __uint_as_float(r[jj + 3]) : 0.f;
-                        }
-                    } else {
-#pragma unroll
-                        for (int cb = 0; cb < 4; cb++) {              // 16-byte pieces: 8 columns each
-                            uint32_t hi[4], lo[4];
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                const int j = half * 32 + cb * 8 + 2 * e;
-                                const float2 lc = *reinterpret_cast<const float2*>(s_Lc + j);
-                                const float a0 = (j <= i) ? ex2(Li - lc.x) * __uint_as_float(r[cb * 8 + 2 * e]) : 0.f;
-                                const float a1 = (j + 1 <= i) ? ex2(Li - lc.y) * __uint_as_float(r[cb * 8 + 2 * e + 1]) : 0.f;
-                                split_pack(a0, a1, hi[e], lo[e]);
-                            }
-                            const uint32_t o = i * 128 + (((half * 4 + cb) ^ (i & 7)) << 4);
-                            *reinterpret_cast<uint4*>(smem + SM_A_HI + o) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                            *reinterpret_cast<uint4*>(smem + SM_A_LO + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-                        }
+                    for (int jj = 0; jj < 32; jj += 4) {
+                        const float4 lc = *reinterpret_cast<const float4*>(Lc + half * 32 + jj);
+                        const int j = half * 32 + jj;
+                        Lm[j * LSTRIDE + i] = (j < i) ? bi * ex2(Li - lc.x) * __uint_as_float(r[jj]) : 0.f;
+                        Lm[(j + 1) * LSTRIDE + i] = (j + 1 < i) ? bi * ex2(Li - lc.y) * __uint_as_float(r[jj + 1]) : 0.f;
+                        Lm[(j + 2) * LSTRIDE + i] = (j + 2 < i) ? bi * ex2(Li - lc.z) * __uint_as_float(r[jj + 2]) : 0.f;
+                        Lm[(j + 3) * LSTRIDE + i] = (j + 3 < i) ? bi * ex2(Li - lc.w) * __uint_as_float(r[jj + 3]) : 0.f;
                     }
                 }
             }
             tc_fence_before_sync();
             if (!group_sync()) break;
 
-            // ---- T = (I + L)^-1: one column per thread (threads 0..63), written as fp32 rows ----
-            if (warp == 0) solve_column<0>(Lm, Tm, tid);
-            else if (warp == 1) solve_column<2>(Lm, Tm, tid);
+            // ---- T = (I + L)^-1: two threads per column ----
+            solve_column(Lm, Tm, tid >> 1, tid & 1, warp);
             if (!group_sync()) break;
             // ---- Tb = T diag(beta), Tg = -Tb diag(gamma) as bf16 hi/lo K-major rows: thread = (row, half of the columns) ----
+            if (c >= 1 && !wait(B_DDONE, (uint32_t)(c - 1))) break;  // the previous chunk's D MMAs have read the old Tb / Tg
             {
                 const int i = tid >> 1, hf = tid & 1;
+                const float* be = g_beta(c);
+                const float* ng = g_ngam(c);
 #pragma unroll
                 for (int cb = 0; cb < 4; cb++) {
                     uint32_t bh[4], bl[4], gh[4], gl[4];
@@ -297,8 +321,8 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     for (int e = 0; e < 4; e += 2) {
                         const int j = hf * 32 + cb * 8 + 2 * e;
                         const float4 t4 = *reinterpret_cast<const float4*>(Tm + i * LSTRIDE + j);
-                        const float4 b4 = *reinterpret_cast<const float4*>(s_beta + j);
-                        const float4 g4 = *reinterpret_cast<const float4*>(s_ngam + j);
+                        const float4 b4 = *reinterpret_cast<const float4*>(be + j);
+                        const float4 g4 = *reinterpret_cast<const float4*>(ng + j);
                         const float v0 = t4.x * b4.x, v1 = t4.y * b4.y, v2 = t4.z * b4.z, v3 = t4.w * b4.w;
                         split_pack(v0, v1, bh[e], bl[e]);
                         split_pack(v2, v3, bh[e + 1], bl[e + 1]);
@@ -314,39 +338,10 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             fence_proxy_async_smem();
             warp_arrive(B_TB);
-
-            // ---- y epilogue: Y^T = P2^T diag(gamma) + A D, transposed through shared memory, 16-byte stores ----
-            if (!wait(B_YDONE, par)) break;
-            tc_fence_after_sync();
-            if (tid == 0 && c + 2 < nchunks) issue_tma(c + 2);       // every reader of this stage (MMAs of chunk c) has finished
-            {
-                __nv_bfloat16* ys = reinterpret_cast<__nv_bfloat16*>(smem + SM_T);       // [64][128]
-#pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    uint32_t p2[32], ad[32];
-                    tmem_ld32(tl + TM_P2 + half * 32, p2);
-                    tmem_ld32(tl + TM_G + half * 32, ad);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int ii = 0; ii < 32; ii++) {
-                        const int i = half * 32 + ii;
-                        ys[i * 128 + tid] = __float2bfloat16_rn(s_gam[i] * __uint_as_float(p2[ii]) + __uint_as_float(ad[ii]));
-                    }
-                }
-                if (!group_sync()) break;
-                __nv_bfloat16* yg = a.y + ((size_t)t0 * a.H + h) * DV;
-#pragma unroll
-                for (int k8 = 0; k8 < 8; k8++) {
-                    const int p = tid + 128 * k8, row = p >> 4, c16 = p & 15;
-                    if (row < nrows)
-                        *reinterpret_cast<uint4*>(yg + (size_t)row * a.H * DV + c16 * 8) = *reinterpret_cast<const uint4*>(ys + row * 128 + c16 * 8);
-                }
-                if (!group_sync()) break;                            // the staging bytes become T of the next chunk
-            }
         }
     } else if (warp < 12) {
         // ============================================================================================================
-        // state-dependent passes between the MMAs: two warps per TMEM lane quadrant, half of the columns each
+        // chain: the state-dependent passes between the MMAs: two warps per TMEM lane quadrant, half of the columns each
         // ============================================================================================================
         const int cw = warp - 4, q = cw & 3, hf = cw >> 2;
         const int r = q * 32 + lane;                                 // value row of this thread
@@ -387,9 +382,9 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             warp_arrive(B_SREADY);
         }
         for (int c = 0; c < nchunks; c++) {
-            const uint32_t par = (uint32_t)c & 1u;
+            const uint32_t par = (uint32_t)c;
             const bool last = c == nchunks - 1;
-            if (*(volatile int*)&s_abort) break;
+            if (aborted()) break;
             const float gC_next = last ? 1.f : ex2(warp_sum(part_next) * LOG2E);
             part_next = decay_part(c + 2);
 
@@ -413,6 +408,7 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             if (!wait(B_DDONE, par)) break;
             tc_fence_after_sync();
             {
+                const float* dec = g_dec(c);
                 uint32_t rr[32], hi[16], lo[16];
                 tmem_ld32(tl + TM_P1 + hf * 32, rr);
                 tmem_wait_ld();
@@ -426,7 +422,7 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
                     for (int e = 0; e < 4; e += 2) {
                         const int jj = cb * 8 + 2 * e;
-                        const float4 d4 = *reinterpret_cast<const float4*>(s_dec + hf * 32 + jj);
+                        const float4 d4 = *reinterpret_cast<const float4*>(dec + hf * 32 + jj);
                         split_pack(__uint_as_float(rr[jj]) * d4.x, __uint_as_float(rr[jj + 1]) * d4.y, ph[e], pl[e]);
                         split_pack(__uint_as_float(rr[jj + 2]) * d4.z, __uint_as_float(rr[jj + 3]) * d4.w, ph[e + 1], pl[e + 1]);
                     }
@@ -440,9 +436,26 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             tc_fence_before_sync();
             warp_arrive(B_DPREADY);
 
-            // ---- new state: bf16 hi/lo pairs for the next chunk's products, fp32 copy pre-scaled by the next gamma_C (or the output) ----
+            // ---- after the state update: scale P2^T by gamma (A D is accumulated on top of it), then the new state ----
             if (!wait(B_SDONE, par)) break;
             tc_fence_after_sync();
+            {
+                const float* gam = g_gam(c);
+                uint32_t rr[32];
+                tmem_ld32(tl + TM_Y + hf * 32, rr);
+                tmem_wait_ld();
+#pragma unroll
+                for (int ii = 0; ii < 32; ii += 4) {
+                    const float4 g4 = *reinterpret_cast<const float4*>(gam + hf * 32 + ii);
+                    rr[ii] = __float_as_uint(__uint_as_float(rr[ii]) * g4.x); rr[ii + 1] = __float_as_uint(__uint_as_float(rr[ii + 1]) * g4.y);
+                    rr[ii + 2] = __float_as_uint(__uint_as_float(rr[ii + 2]) * g4.z); rr[ii + 3] = __float_as_uint(__uint_as_float(rr[ii + 3]) * g4.w);
+                }
+                tmem_st32(tl + TM_Y + hf * 32, rr);
+                tmem_wait_st();
+            }
+            tc_fence_before_sync();
+            warp_arrive(B_YSCALED);
+            // bf16 hi/lo pairs of the new state for the next chunk's products, fp32 copy pre-scaled by the next gamma_C (or the output)
 #pragma unroll
             for (int blk = 0; blk < 2; blk++) {
                 uint32_t rr[32], hi[16], lo[16];
@@ -470,91 +483,171 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 warp_arrive(B_SREADY);
             }
         }
-    } else if (lane == 0) {
+    } else if (warp == 12) {
         // ============================================================================================================
         // the MMA issuer (one thread)
         // ============================================================================================================
-        constexpr uint32_t I64 = idesc_bf16(128, 64, 0, 0);          // N = 64, A and B K-major (A may also come from TMEM)
-        constexpr uint32_t I64_AMN = idesc_bf16(128, 64, 1, 0);      // N = 64, A read MN-major (V as V^T)
-        constexpr uint32_t I128_BMN = idesc_bf16(128, 128, 0, 1);    // N = 128, B read MN-major (K as the [tokens x dk] factor)
-        issue_tma(0);
-        if (nchunks > 1) issue_tma(1);
-        for (int c = 0; c < nchunks; c++) {
-            const uint32_t par = (uint32_t)c & 1u;
-            const uint32_t st = sbase + (c & 1) * SM_STAGE;
-            if (*(volatile int*)&s_abort) break;
-            // ---- G = [K; Q] K^T ----
-            if (!wait(B_INPUTS, par)) break;
-            tc_fence_after_sync();
-#pragma unroll
-            for (int ks = 0; ks < 8; ks++) {
-                const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-                const uint64_t d = smem_desc_sw128(st + off, 16, 1024);
-                mma_ss(tb + TM_G, d, d, I64, ks > 0);
-            }
-            mma_commit(bar(B_GDONE));
-            // ---- P1^T = S0 K^T, P2^T = S0 Q^T (S0 = hi + lo from TMEM) ----
-            if (!wait(B_SREADY, par)) break;
-            tc_fence_after_sync();
-#pragma unroll
-            for (int part = 0; part < 2; part++) {
-                const uint32_t acol = part ? TM_SLO : TM_SHI;
+        if (lane == 0) {
+            constexpr uint32_t I64 = idesc_bf16(128, 64, 0, 0);      // N = 64, A and B K-major (A may also come from TMEM)
+            constexpr uint32_t I64_AMN = idesc_bf16(128, 64, 1, 0);  // N = 64, A read MN-major (V as V^T)
+            constexpr uint32_t I128_BMN = idesc_bf16(128, 128, 0, 1);// N = 128, B read MN-major (K as the [tokens x dk] factor)
+            auto issue_G = [&](int c) {                              // G = [K; Q] K^T of chunk c
+                const uint32_t st = sbase + (c & 1) * SM_STAGE;
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {
                     const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-                    mma_ts(tb + TM_P1, tb + acol + ks * 8, smem_desc_sw128(st + off, 16, 1024), I64, (part | ks) != 0);
+                    const uint64_t d = smem_desc_sw128(st + off, 16, 1024);
+                    mma_ss(tb + TM_G, d, d, I64, ks > 0);
                 }
-            }
-            mma_commit(bar(B_P1DONE));
+                mma_commit(bar(B_GDONE));
+            };
+            issue_tma(0);
+            if (nchunks > 1) issue_tma(1);
+            bool ok = wait(B_INPUTS, 0);
+            if (ok) { tc_fence_after_sync(); issue_G(0); }
+            for (int c = 0; ok && c < nchunks; c++) {
+                const uint32_t par = (uint32_t)c;
+                const uint32_t st = sbase + (c & 1) * SM_STAGE;
+                if (aborted()) break;
+                // ---- P1^T = S0 K^T (S0 = hi + lo from TMEM) ----
+                if (!wait(B_SREADY, par)) break;
+                tc_fence_after_sync();
 #pragma unroll
-            for (int part = 0; part < 2; part++) {
-                const uint32_t acol = part ? TM_SLO : TM_SHI;
+                for (int part = 0; part < 2; part++) {
+                    const uint32_t acol = part ? TM_SLO : TM_SHI;
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++) {
-                    const uint32_t off = 8192 + (ks >> 2) * 16384 + (ks & 3) * 32;
-                    mma_ts(tb + TM_P2, tb + acol + ks * 8, smem_desc_sw128(st + off, 16, 1024), I64, (part | ks) != 0);
+                    for (int ks = 0; ks < 8; ks++) {
+                        const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
+                        mma_ts(tb + TM_P1, tb + acol + ks * 8, smem_desc_sw128(st + off, 16, 1024), I64, (part | ks) != 0);
+                    }
                 }
+                mma_commit(bar(B_P1DONE));
+                // ---- G of the next chunk, so that the solver works one chunk ahead ----
+                if (c + 1 < nchunks) {
+                    if (!wait(B_INPUTS, par + 1) || !wait(B_GFREE, par)) break;
+                    tc_fence_after_sync();
+                    issue_G(c + 1);
+                }
+                // ---- D^T = V^T Tb^T + P1^T Tg^T (the P1 columns become the D accumulator once P1 has been split) ----
+                if (!wait(B_TB, par) || !wait(B_ZREADY, par)) break;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int part = 0; part < 2; part++) {
+                    const uint32_t bsm = sbase + (part ? SM_TB_LO : SM_TB_HI);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++)
+                        mma_ss(tb + TM_P1, smem_desc_sw128(st + SM_V + ks * 2048, 8192, 1024), smem_desc_sw128(bsm + ks * 32, 16, 1024), I64_AMN,
+                               (part | ks) != 0);
+                }
+#pragma unroll
+                for (int term = 0; term < 3; term++) {
+                    const uint32_t acol = term == 1 ? TM_ZLO : TM_ZHI;
+                    const uint32_t bsm = sbase + (term == 2 ? SM_TG_LO : SM_TG_HI);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) mma_ts(tb + TM_P1, tb + acol + ks * 8, smem_desc_sw128(bsm + ks * 32, 16, 1024), I64, 1);
+                }
+                mma_commit(bar(B_DDONE));
+                // ---- P2^T = S0 Q^T (once the previous y has left its columns), then the state update S += Dp^T K ----
+                if (!wait(B_DPREADY, par)) break;
+                if (c >= 1 && !wait(B_YFREE, par - 1)) break;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int part = 0; part < 2; part++) {
+                    const uint32_t acol = part ? TM_SLO : TM_SHI;
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++) {
+                        const uint32_t off = 8192 + (ks >> 2) * 16384 + (ks & 3) * 32;
+                        mma_ts(tb + TM_Y, tb + acol + ks * 8, smem_desc_sw128(st + off, 16, 1024), I64, (part | ks) != 0);
+                    }
+                }
+#pragma unroll
+                for (int part = 0; part < 2; part++) {
+                    const uint32_t asm_ = sbase + (part ? SM_DP_LO : SM_DP_HI);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++)
+                        mma_ss(tb + TM_S, smem_desc_sw128(asm_ + ks * 32, 16, 1024), smem_desc_sw128(st + ks * 2048, 16384, 1024), I128_BMN, 1);
+                }
+                mma_commit(bar(B_SDONE));
+                // ---- Y^T = gamma-scaled P2^T + D^T A^T ----
+                if (!wait(B_AREADY, par) || !wait(B_YSCALED, par)) break;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int term = 0; term < 3; term++) {
+                    const uint32_t acol = term == 1 ? TM_ZLO : TM_ZHI;
+                    const uint32_t bsm = sbase + (term == 2 ? SM_A_LO : SM_A_HI);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) mma_ts(tb + TM_Y, tb + acol + ks * 8, smem_desc_sw128(bsm + ks * 32, 16, 1024), I64, 1);
+                }
+                mma_commit(bar(B_YDONE));
             }
-            // ---- D^T = V^T Tb^T + P1^T Tg^T (the P1 columns become the D accumulator once P1 has been split) ----
-            if (!wait(B_TB, par)) break;
-            if (!wait(B_ZREADY, par)) break;
+        }
+    } else {
+        // ============================================================================================================
+        // output: A from Q K^T (the two warps that own TMEM lanes 64..127), y rows, TMA of the chunk after next
+        // ============================================================================================================
+        const int q = warp & 3;
+        const int r = q * 32 + lane;
+        const uint32_t tl = tb + ((uint32_t)(q * 32) << 16);
+        for (int c = 0; c < nchunks; c++) {
+            const uint32_t par = (uint32_t)c;
+            const int t0 = t_begin + c * CH;
+            const int nrows = min(CH, t_end - t0);
+            if (aborted()) break;
+            // ---- A = lower_incl(exp(Lc_i - Lc_j) Q K^T) as bf16 hi/lo K-major rows (the previous chunk's A D has completed) ----
+            if (!wait(B_GDONE, par)) break;
             tc_fence_after_sync();
+            if (q >= 2) {
+                const int i = r - 64;
+                const float* Lc = g_Lc(c);
+                const float Li = Lc[i];
 #pragma unroll
-            for (int part = 0; part < 2; part++) {
-                const uint32_t bsm = sbase + (part ? SM_TB_LO : SM_TB_HI);
+                for (int half = 0; half < 2; half++) {
+                    uint32_t rr[32];
+                    tmem_ld32(tl + TM_G + half * 32, rr);
+                    tmem_wait_ld();
 #pragma unroll
-                for (int ks = 0; ks < 4; ks++)
-                    mma_ss(tb + TM_P1, smem_desc_sw128(st + SM_V + ks * 2048, 8192, 1024), smem_desc_sw128(bsm + ks * 32, 16, 1024), I64_AMN,
-                           (part | ks) != 0);
+                    for (int cb = 0; cb < 4; cb++) {                  // 16-byte pieces: 8 columns each
+                        uint32_t hi[4], lo[4];
+#pragma unroll
+                        for (int e = 0; e < 4; e += 2) {
+                            const int jj = cb * 8 + 2 * e, j = half * 32 + jj;
+                            const float4 lc = *reinterpret_cast<const float4*>(Lc + j);
+                            const float a0 = (j <= i) ? ex2(Li - lc.x) * __uint_as_float(rr[jj]) : 0.f;
+                            const float a1 = (j + 1 <= i) ? ex2(Li - lc.y) * __uint_as_float(rr[jj + 1]) : 0.f;
+                            const float a2 = (j + 2 <= i) ? ex2(Li - lc.z) * __uint_as_float(rr[jj + 2]) : 0.f;
+                            const float a3 = (j + 3 <= i) ? ex2(Li - lc.w) * __uint_as_float(rr[jj + 3]) : 0.f;
+                            split_pack(a0, a1, hi[e], lo[e]);
+                            split_pack(a2, a3, hi[e + 1], lo[e + 1]);
+                        }
+                        const uint32_t o = i * 128 + (((half * 4 + cb) ^ (i & 7)) << 4);
+                        *reinterpret_cast<uint4*>(smem + SM_A_HI + o) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                        *reinterpret_cast<uint4*>(smem + SM_A_LO + o) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    }
+                }
+                fence_proxy_async_smem();
+                tc_fence_before_sync();
+                warp_arrive(B_AREADY);
+                warp_arrive(B_GFREE);
             }
-#pragma unroll
-            for (int term = 0; term < 3; term++) {
-                const uint32_t acol = term == 1 ? TM_ZLO : TM_ZHI;
-                const uint32_t bsm = sbase + (term == 2 ? SM_TG_LO : SM_TG_HI);
-#pragma unroll
-                for (int ks = 0; ks < 4; ks++) mma_ts(tb + TM_P1, tb + acol + ks * 8, smem_desc_sw128(bsm + ks * 32, 16, 1024), I64, 1);
-            }
-            mma_commit(bar(B_DDONE));
-            // ---- state update S += Dp^T K, then A D into the G columns ----
-            if (!wait(B_DPREADY, par)) break;
+            // ---- y[t0 + i, h, v] = Y^T[v][i]: each lane owns one value row, a warp store covers 64 contiguous bytes ----
+            if (!wait(B_YDONE, par)) break;
             tc_fence_after_sync();
+            if (warp == 13 && lane == 0 && c + 2 < nchunks) issue_tma(c + 2);    // every reader of this stage (MMAs of chunk c) has finished
+            {
+                __nv_bfloat16* yp = a.y + ((size_t)t0 * a.H + h) * DV + r;
+                uint32_t y0[32], y1[32];
+                tmem_ld32(tl + TM_Y, y0);
+                tmem_ld32(tl + TM_Y + 32, y1);
+                tmem_wait_ld();
+                tc_fence_before_sync();
+                warp_arrive(B_YFREE);                                // the columns may take the next chunk's P2
 #pragma unroll
-            for (int part = 0; part < 2; part++) {
-                const uint32_t asm_ = sbase + (part ? SM_DP_LO : SM_DP_HI);
+                for (int ii = 0; ii < 32; ii++)
+                    if (ii < nrows) yp[(size_t)ii * a.H * DV] = __float2bfloat16_rn(__uint_as_float(y0[ii]));
 #pragma unroll
-                for (int ks = 0; ks < 4; ks++)
-                    mma_ss(tb + TM_S, smem_desc_sw128(asm_ + ks * 32, 16, 1024), smem_desc_sw128(st + ks * 2048, 16384, 1024), I128_BMN, 1);
+                for (int ii = 0; ii < 32; ii++)
+                    if (32 + ii < nrows) yp[(size_t)(32 + ii) * a.H * DV] = __float2bfloat16_rn(__uint_as_float(y1[ii]));
             }
-            mma_commit(bar(B_SDONE));
-#pragma unroll
-            for (int term = 0; term < 3; term++) {
-                const uint32_t acol = term == 1 ? TM_ZLO : TM_ZHI;
-                const uint32_t bsm = sbase + (term == 2 ? SM_A_LO : SM_A_HI);
-#pragma unroll
-                for (int ks = 0; ks < 4; ks++)
-                    mma_ts(tb + TM_G, tb + acol + ks * 8, smem_desc_sw128(bsm + ks * 32, 16, 1024), I64, (term | ks) != 0);
-            }
-            mma_commit(bar(B_YDONE));
         }
     }
     tc_fence_before_sync();
@@ -603,7 +696,7 @@ int launch_prefill(const void* q, const void* k, const void* v, const PrefillArg
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    const int smem = SM_TOTAL + 1024;
+    const int smem = SM_TOTAL;
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         if (cudaFuncSetAttribute(gdn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return check_launch("gdn_prefill smem attribute");

@@ -21,15 +21,17 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+// One poll: the thread is suspended by the hardware until the phase completes or ~`hint_ns` have passed, so a waiting warp
+// does not compete for issue slots with the warps that do the work.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns = 20000u) {
     uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls (each poll itself blocks for a hardware-defined short time) and returns false.
-// The caller records the failure and leaves the kernel instead of spinning for ever on a shared GPU.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = 4000000u) {
+// Bounded wait: gives up after `limit` polls and returns false.  The caller records the failure and leaves the kernel
+// instead of spinning for ever on a shared GPU.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = 200000u) {
     for (uint32_t i = 0; i < limit; i++)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
