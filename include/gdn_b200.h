@@ -120,6 +120,22 @@ int gqa_decode_paged(const void* q, const void* k_new, const void* v_new, void* 
                      const int* ctx_len, void* out, void* workspace, size_t workspace_bytes, int B, int M, int page_size,
                      int max_pages, int n_pages, int max_ctx, void* stream);
 
+/* gqa_decode_paged for callers that cannot provide a workspace because they cannot allocate device memory: an operator
+ * plugged into a serving runtime that reserved the whole device up front and forbids allocation calls on its request path, or
+ * a plain C caller that has no allocator of its own to size a workspace with.  This entry point has no counterpart in the
+ * reference; it exists only for such hosts.  Same arguments and results as gqa_decode_paged, minus the workspace: the
+ * split-KV partials go to a 12 MiB array built into the library (held by every GPU that loads the library until the process
+ * exits).  Nothing is allocated or freed, here or in anything it calls.
+ *   Limit: B * 2 * ceil(max_ctx / split) partials must fit the array (762 of them; e.g. B = 16 at max_ctx = 8192 needs 704).
+ *          Larger problems return GDN_E_SHAPE with a message that names the limit; use gqa_decode_paged for them.
+ *   First call on a device: looks up the array's device address (cudaGetSymbolAddress, with that device current).  Make that
+ *          first call outside any stream capture.
+ *   Sharing: all calls on a device use the same array, which keeps the previous call's contents.  Nothing in it needs
+ *          clearing between calls, but two calls that run concurrently on one GPU (different streams) corrupt each other. */
+int gqa_decode_paged_static(const void* q, const void* k_new, const void* v_new, void* k_pages, void* v_pages, const int* block_table,
+                            const int* ctx_len, void* out, int B, int M, int page_size, int max_pages, int n_pages, int max_ctx,
+                            void* stream);
+
 /* dst.flat[d0 + y*dstride + i] = src.flat[s0 + y*sstride + i] for i < n, y < ny; offsets in elements of elem_size (2 or 4) bytes.
  * Replaces: blit, qwen35/batch.py:349-372. */
 int gdn_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,

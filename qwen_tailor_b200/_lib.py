@@ -34,6 +34,7 @@ SIGNATURES = {
     "gdn_deltanet_bm": (I, [P, LL, P, P, P, P, P, P, P, P, I, P, I, I, P]),
     "gqa_decode_workspace_bytes": (SZ, [I, I]),
     "gqa_decode_paged": (I, [P, P, P, P, P, P, P, P, P, SZ, I, I, I, I, I, I, P]),
+    "gqa_decode_paged_static": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
     "gdn_state_copy": (I, [P, P, I, LL, LL, LL, I, LL, LL, P]),
 }
 

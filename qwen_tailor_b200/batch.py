@@ -61,6 +61,30 @@ def attn_paged(q, k_new, v_new, k_pages, v_pages, block_table, ctx_len, M=1, max
     return o
 
 
+def attn_paged_static(q, k_new, v_new, k_pages, v_pages, block_table, ctx_len, M=1, max_ctx=None):
+    """``attn_paged`` without any allocation on the way to the kernel except the output tensor: the split-KV partials go to a
+    12 MiB scratch array built into the library instead of a torch workspace.  Meant for hosts that may not allocate device
+    memory while serving (their C callers pass a preallocated output and use the C entry point ``gqa_decode_paged_static``
+    directly).  Raises ValueError when the batch needs more than the 762 partials the array holds.  Calls that overlap on one
+    GPU share the array and must not run concurrently; the first call on a device should happen outside stream capture."""
+    _lib.require_cuda(q, k_new, v_new, k_pages, v_pages, block_table, ctx_len)
+    R, H, D = q.shape
+    n_pages, KV, page_size, _ = k_pages.shape
+    if (H, KV, D) != (8, 2, 256) or not 1 <= M <= 4 or R % M:
+        raise ValueError(f"attn: only 8 query heads, 2 KV heads, head_dim 256 and 1 <= M <= 4 are supported (H={H}, KV={KV}, D={D}, M={M})")
+    B = R // M
+    for t in (q, k_new, v_new, k_pages, v_pages):
+        assert t.dtype == torch.bfloat16 and t.is_contiguous()
+    assert block_table.dtype == torch.int32 and ctx_len.dtype == torch.int32 and block_table.is_contiguous()
+    max_pages = block_table.shape[1]
+    if max_ctx is None:
+        max_ctx = max_pages * page_size
+    o = torch.empty((R, H, D), dtype=torch.bfloat16, device=q.device)
+    check(_lib.load().gqa_decode_paged_static(ptr(q), ptr(k_new), ptr(v_new), ptr(k_pages), ptr(v_pages), ptr(block_table), ptr(ctx_len), ptr(o),
+                                              B, M, page_size, max_pages, n_pages, max_ctx, stream_ptr(q.device)), "attn (static scratch)")
+    return o
+
+
 def attn_b(q, k, v, Kp, Vp, slots, pos, M=1):
     """q [R,H,D], k / v [R,KV,D] (normed + roped), pools [S+1,KV,Lmax,D]; R = B*M rows (row b*M+j = position pos[b]+j of slot
     slots[b]; slots / pos int32 [B]).  Returns o [R,H,D] bf16 and appends k / v at pos[b]+j (in place)  (batch.py:230-237).

@@ -190,6 +190,24 @@ int gqa_decode_paged(const void* q, const void* k_new, const void* v_new, void* 
     return launch_gqa_decode(a, max_ctx, static_cast<cudaStream_t>(stream));
 }
 
+int gqa_decode_paged_static(const void* q, const void* k_new, const void* v_new, void* k_pages, void* v_pages, const int* block_table,
+                            const int* ctx_len, void* out, int B, int M, int page_size, int max_pages, int n_pages, int max_ctx, void* stream) {
+    REQUIRE(q && k_new && v_new && k_pages && v_pages && block_table && ctx_len && out, GDN_E_NULL, "gqa_decode_paged_static: null pointer");
+    REQUIRE(B >= 0 && M >= 1 && M <= 4, GDN_E_SHAPE, "gqa_decode_paged_static: B=%d M=%d (1 <= M <= 4)", B, M);
+    REQUIRE(page_size > 0 && max_pages > 0 && n_pages > 0 && max_ctx >= 0, GDN_E_SHAPE,
+            "gqa_decode_paged_static: page_size=%d max_pages=%d n_pages=%d max_ctx=%d", page_size, max_pages, n_pages, max_ctx);
+    REQUIRE(aligned16(q) && aligned16(k_new) && aligned16(v_new) && aligned16(k_pages) && aligned16(v_pages) && aligned16(out), GDN_E_ALIGN,
+            "gqa_decode_paged_static: tensors must be 16-byte aligned");
+    AttnArgs a{};
+    a.q = static_cast<const __nv_bfloat16*>(q); a.k_new = static_cast<const __nv_bfloat16*>(k_new); a.v_new = static_cast<const __nv_bfloat16*>(v_new);
+    a.k_pages = static_cast<__nv_bfloat16*>(k_pages); a.v_pages = static_cast<__nv_bfloat16*>(v_pages);
+    a.block_table = block_table; a.ctx_len = ctx_len; a.out = static_cast<__nv_bfloat16*>(out);
+    a.B = B; a.M = M; a.page_size = page_size; a.max_pages = max_pages; a.n_pages = n_pages;
+    a.status = status_ptr();
+    REQUIRE(a.status, GDN_E_LAUNCH, "gqa_decode_paged_static: no CUDA device");
+    return launch_gqa_decode_static(a, max_ctx, static_cast<cudaStream_t>(stream));
+}
+
 int gdn_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,
                    long long sstride, void* stream) {
     REQUIRE(dst && src, GDN_E_NULL, "gdn_state_copy: null pointer");

@@ -326,4 +326,45 @@ int launch_gqa_decode(AttnArgs a, int max_ctx, cudaStream_t stream) {
     return check_launch("gqa_decode_merge");
 }
 
+// ----------------------------------------------------------------------------------------------------------------------
+// Variant for callers that cannot allocate device memory: the split-KV partials go to a fixed array that lives in the library
+// image instead of a caller-provided workspace.  Every GPU that loads the library holds these 12 MiB until the process exits.
+// The array is shared by all calls on a device and keeps whatever the last call left in it; nothing in it has to start at zero
+// (every partial that the merge kernel reads was written by the split kernel of the same call), but two calls that overlap on
+// the GPU (different streams) would overwrite each other's partials.
+// ----------------------------------------------------------------------------------------------------------------------
+constexpr int STATIC_PARTIALS = 762;                                   // (sequence, kv head, split) triples that fit
+static __device__ __align__(256) float g_static_partials[(size_t)STATIC_PARTIALS * PART_STRIDE];      // 12 MiB
+
+int gqa_static_max_partials() { return STATIC_PARTIALS; }
+
+int launch_gqa_decode_static(AttnArgs a, int max_ctx, cudaStream_t stream) {
+    if (a.B <= 0) return GDN_OK;
+    int sk, ms;
+    gqa_split_plan(a.B, max_ctx, &sk, &ms);
+    const long long need = (long long)a.B * ATT_KV * ms;
+    if (need > STATIC_PARTIALS) {
+        set_error("gqa_decode_paged_static: B=%d sequences of up to %d tokens need %lld split partials, the built-in scratch holds %d "
+                  "(use gqa_decode_paged with a workspace of gqa_decode_workspace_bytes() instead)", a.B, max_ctx, need, STATIC_PARTIALS);
+        return GDN_E_SHAPE;
+    }
+    // In host code the array's name is only a handle: the device address has to be asked for, once per device, with that device
+    // current.  The first call on a device does it (and should therefore come before any stream capture).
+    static float* addr[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return check_launch("gqa_decode_paged_static: device");
+    if (!addr[dev]) {
+        float* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_partials);
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            set_error("gqa_decode_paged_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return GDN_E_LAUNCH;
+        }
+        addr[dev] = p;
+    }
+    a.part = addr[dev];
+    return launch_gqa_decode(a, max_ctx, stream);
+}
+
 }  // namespace gdn

@@ -55,6 +55,8 @@ struct AttnArgs {
 
 size_t gqa_workspace_bytes(int B, int max_ctx);
 int launch_gqa_decode(AttnArgs a, int max_ctx, cudaStream_t stream);
+int launch_gqa_decode_static(AttnArgs a, int max_ctx, cudaStream_t stream);
+int gqa_static_max_partials();
 
 // ---- gdn_prefill_sm100.cu ----
 struct PrefillArgs {

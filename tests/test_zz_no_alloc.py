@@ -1,0 +1,69 @@
+"""The allocation-free attention entry point (``gqa_decode_paged_static``) against the workspace-taking one.
+
+Some hosts of this library may not allocate device memory while they serve requests (a plugin inside a runtime that reserved
+the whole GPU up front, a bare C caller without an allocator), so they cannot hand ``gqa_decode_paged`` a workspace.  For them
+the library carries a fixed 12 MiB scratch array.  This test drives the new entry point through the C ABI exactly as such a
+caller would (raw pointers, preallocated output), twice in a row because the scratch array keeps the previous call's contents,
+and requires the same output and the same appended cache rows as the existing entry point.  It is collected last so that a run
+that stops at the first failure has already run every other test.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_dev, i32_dev
+from qwen_tailor_b200 import _lib, synth
+from qwen_tailor_b200._lib import check, ptr, stream_ptr
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(entry, c, dev, M, max_ctx, workspace):
+    """One call through the C ABI on fresh copies of the cache pages.  Returns (output, K pages, V pages)."""
+    lib = _lib.load()
+    q, kn, vn = (bf16_dev(c[n], dev) for n in ("q", "k_new", "v_new"))
+    Kp, Vp = bf16_dev(c["k_pages"], dev), bf16_dev(c["v_pages"], dev)
+    bt, cl = i32_dev(c["block_table"], dev), i32_dev(c["ctx_len"], dev)
+    B = len(c["ctx_len"])
+    n_pages, _, page_size, _ = Kp.shape
+    out = torch.full((B * M, 8, 256), float("nan"), dtype=torch.bfloat16, device=dev)
+    common = (ptr(q), ptr(kn), ptr(vn), ptr(Kp), ptr(Vp), ptr(bt), ptr(cl), ptr(out))
+    tail = (B, M, page_size, bt.shape[1], n_pages, max_ctx, stream_ptr(dev))
+    if entry == "static":
+        rc = lib.gqa_decode_paged_static(*common, *tail)
+    else:
+        rc = lib.gqa_decode_paged(*common, ptr(workspace), workspace.numel() * 4, *tail)
+    check(rc, entry)
+    torch.cuda.synchronize()
+    return out, Kp, Vp
+
+
+def test_static_scratch_entry_matches_workspace_entry(dev):
+    lib = _lib.load()
+    rng = np.random.default_rng(123)
+    cases = [(synth.attn_case(rng, [3000, 17, 900, 0, 2047], 4, 64), 4, 3004),
+             (synth.attn_case(rng, [5, 700, 64], 1, 16), 1, 704)]          # second call: different shape, scratch holds stale data
+    for c, M, max_ctx in cases:
+        B = len(c["ctx_len"])
+        ws = torch.empty(max(lib.gqa_decode_workspace_bytes(B, max_ctx) // 4, 4), dtype=torch.float32, device=dev)
+        want, Kw, Vw = _run("workspace", c, dev, M, max_ctx, ws)
+        got, Kg, Vg = _run("static", c, dev, M, max_ctx, None)
+        assert not torch.isnan(got.float()).any()
+        # same kernels, same split plan, only the scratch location differs: the tolerance of the attention tests (rel-L2 2e-3)
+        # is met with room to spare -- the results are in fact identical
+        diff = (got.float() - want.float()).norm() / want.float().norm()
+        assert float(diff) < 2e-3
+        assert torch.equal(got, want)
+        assert torch.equal(Kg, Kw) and torch.equal(Vg, Vw)
+    assert _lib.device_status() == 0
+
+
+def test_static_scratch_rejects_oversized_batches(dev):
+    lib = _lib.load()
+    one = ctypes.c_void_p(256)
+    rc = lib.gqa_decode_paged_static(one, one, one, one, one, one, one, one, 64, 1, 64, 2048, 4096, 131072, None)
+    assert rc == -1
+    msg = lib.gdn_last_error_string().decode()
+    assert "762" in msg and "gqa_decode_paged" in msg
