@@ -142,6 +142,19 @@ def time_region(torch, fn, iters, dist=None):
     return ms
 
 
+def graphed(torch, step, warm=3):
+    """Run `step` a few times, capture it into a CUDA graph (as the reference compiles its step) and return the replay callable."""
+    for _ in range(warm):
+        step()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    for _ in range(warm):
+        g.replay()
+    return g.replay
+
+
 def bench_decode(torch, dev, args, dist, peaks, B=B_DECODE, n_layers=N_LAYERS, with_e2e=True):
     from qwen_tailor_b200.batch import deltanet_b
     layers = make_decode_layers(torch, dev, B, n_layers, seed=1 + (dist.get_rank() if dist else 0))
@@ -189,7 +202,7 @@ def bench_decode(torch, dev, args, dist, peaks, B=B_DECODE, n_layers=N_LAYERS, w
     return out
 
 
-def bench_attention(torch, dev, args, peaks):
+def bench_attention(torch, dev, args, peaks, n_layers=6):
     """Configuration 5, attention part: B=16, M=4 rows per sequence, 6 layers, paged cache, ctx ~ U[1024, 8192]."""
     import numpy as np
     from qwen_tailor_b200 import synth
@@ -207,7 +220,7 @@ def bench_attention(torch, dev, args, peaks):
     g.manual_seed(11)
     rn = lambda *s: torch.randn(s, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
     layers = [dict(K=rn(n_pages, 2, page, 256), V=rn(n_pages, 2, page, 256), q=rn(B * M, 8, 256), k=rn(B * M, 2, 256), v=rn(B * M, 2, 256))
-              for _ in range(6)]
+              for _ in range(n_layers)]
     bt = torch.from_numpy(table).to(dev)
     cl = torch.from_numpy(ctx).to(dev)
     mc = int(ctx.max())
@@ -216,23 +229,21 @@ def bench_attention(torch, dev, args, peaks):
         for L in layers:
             attn_paged(L["q"], L["k"], L["v"], L["K"], L["V"], bt, cl, M=M, max_ctx=mc)
 
-    for _ in range(3):
-        step()
-    ms = time_region(torch, step, args.steps) / args.steps
-    byts = 6 * float(ctx.sum()) * 2048
+    ms = time_region(torch, graphed(torch, step), args.steps) / args.steps
+    byts = n_layers * float(ctx.sum()) * 2048
     gbs = byts / (ms * 1e-3) / 1e9
-    return dict(workload="GQA decode attention, config 5: B=16, M=4, 6 layers, paged bf16 KV, ctx~U[1024,8192]", ms_per_step=ms,
+    return dict(workload=f"GQA decode attention, config 5: B=16, M=4, {n_layers} layers, paged bf16 KV, ctx~U[1024,8192]", ms_per_step=ms,
                 kv_gb=byts / 1e9, roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"]))
 
 
-def bench_verify(torch, dev, args, peaks):
+def bench_verify(torch, dev, args, peaks, n_layers=N_LAYERS):
     """Configuration 5, GDN part: B=16 sequences x M=4 chained tokens through 18 layers, per-token fp32 snapshots in place."""
     from qwen_tailor_b200.batch_spec import deltanet_bm
     B, M = 16, 4
     g = torch.Generator(device=dev)
     g.manual_seed(11)
     layers = []
-    for _ in range(N_LAYERS):
+    for _ in range(n_layers):
         layers.append(dict(
             proj=torch.randn((B * M, PW), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16),
             conv=torch.randn(((B + 1) * 2, M, 3, CD), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16),
@@ -248,16 +259,14 @@ def bench_verify(torch, dev, args, peaks):
         for L in layers:
             deltanet_bm(L["proj"], L["conv"], L["conv_w"], L["A_log"], L["dt_bias"], L["ssm"], ss, sels, pars, M)
 
-    for _ in range(3):
-        step()
-    ms = time_region(torch, step, args.steps) / args.steps
+    ms = time_region(torch, graphed(torch, step), args.steps) / args.steps
     per = (1 + M) * STATE_BYTES + M * (CD * 2 + 3 * CD * 2 + HV * DV * 2) + 3 * CD * 2
-    gbs = N_LAYERS * B * per / (ms * 1e-3) / 1e9
+    gbs = n_layers * B * per / (ms * 1e-3) / 1e9
     return dict(workload="GDN speculative verify, config 5: B=16, M=4, 18 layers, snapshots [B,4,16,128,128] fp32 in place", ms_per_step=ms,
                 roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"]))
 
 
-def bench_prefill(torch, dev, args, peaks, T=2048):
+def bench_prefill(torch, dev, args, peaks, T=2048, n_layers=N_LAYERS):
     """Configuration 3: one sequence of T tokens, chunk 64, applied as 18 independent layers (one packed launch)."""
     try:
         from qwen_tailor_b200.gdn_nax import gdn_chunked_varlen
@@ -265,7 +274,7 @@ def bench_prefill(torch, dev, args, peaks, T=2048):
         return None
     g = torch.Generator(device=dev)
     g.manual_seed(100)
-    n = N_LAYERS
+    n = n_layers
     rn = lambda *s: torch.randn(s, generator=g, device=dev, dtype=torch.float32)
     unit = lambda x: x / x.norm(dim=-1, keepdim=True)
     sets = []
@@ -291,7 +300,7 @@ def bench_prefill(torch, dev, args, peaks, T=2048):
     toks = n * T
     tflops = toks * PREFILL_FLOP_PER_TOKEN_LAYER / (ms * 1e-3) / 1e12
     gbs = (toks * PREFILL_BYTES_PER_TOKEN_LAYER + n * STATE_BYTES) / (ms * 1e-3) / 1e9
-    return dict(workload=f"GDN chunked prefill, config 3: B=1, T={T}, chunk 64, 18 independent layers, zero initial state", ms_per_step=ms,
+    return dict(workload=f"GDN chunked prefill, config 3: B=1, T={T}, chunk 64, {n} independent layers, zero initial state", ms_per_step=ms,
                 tokens_per_s=toks / (ms * 1e-3),
                 roofline=dict(bound="tensor", achieved=tflops, peak=peaks["bf16_tflops"], unit="TFLOP/s", frac=tflops / peaks["bf16_tflops"]),
                 hbm=dict(achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"]))
@@ -360,6 +369,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the additional workloads (prefill, verify, attention, small batches)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--case", default=None, choices=["prefill", "attention", "verify"],
+                    help="run only this small workload a few times and print its line (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
@@ -381,6 +392,17 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
     peaks = measured_peaks()
+
+    if args.case:
+        a2 = argparse.Namespace(steps=max(1, min(args.steps, 3)), warmup=3)
+        if args.case == "prefill":
+            out = bench_prefill(torch, dev, a2, peaks, n_layers=9)       # 9 x 16 chains = one wave of 144 blocks, 0.3 GB of inputs
+        elif args.case == "attention":
+            out = bench_attention(torch, dev, a2, peaks, n_layers=2)
+        else:
+            out = bench_verify(torch, dev, a2, peaks, n_layers=4)
+        print(json.dumps(out))
+        return
 
     sampler = ClockSampler(local)
     sampler.start()

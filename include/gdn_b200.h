@@ -126,7 +126,7 @@ int gqa_decode_paged(const void* q, const void* k_new, const void* v_new, void* 
  * reference; it exists only for such hosts.  Same arguments and results as gqa_decode_paged, minus the workspace: the
  * split-KV partials go to a 12 MiB array built into the library (held by every GPU that loads the library until the process
  * exits).  Nothing is allocated or freed, here or in anything it calls.
- *   Limit: B * 2 * ceil(max_ctx / split) partials must fit the array (762 of them; e.g. B = 16 at max_ctx = 8192 needs 704).
+ *   Limit: B * 2 * ceil(max_ctx / split) partials must fit the array (762 of them; e.g. B = 16 at max_ctx = 8192 needs 224).
  *          Larger problems return GDN_E_SHAPE with a message that names the limit; use gqa_decode_paged for them.
  *   First call on a device: looks up the array's device address (cudaGetSymbolAddress, with that device current).  Make that
  *          first call outside any stream capture.

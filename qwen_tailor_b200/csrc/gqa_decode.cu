@@ -12,7 +12,9 @@
 //     merges them.
 //   * GQA packing: the 4 query heads of a KV head times the M <= 4 chained rows form the 16 rows of a warp-level
 //     m16n8k16 bf16 MMA, so each K/V byte is read once for up to 16 query rows (at M = 4 plain FMAs could not keep up with
-//     HBM).  Each of the 4 warps owns 16 of the 64 keys of a tile and keeps its own online-softmax state.
+//     HBM).  Each of the 8 warps owns 8 of the 64 keys of a tile (scores by m16n8k16, P.V by m16n8k8) and keeps its own
+//     online-softmax state; eight warps rather than four because the per-tile dependency chains (16 chained score MMAs,
+//     the softmax shuffles) are latency-bound and need other warps to hide behind.
 //   * K/V tiles (64 keys x 512 B) are gathered page by page with 16-byte cp.async into XOR-swizzled shared memory, three
 //     stages (192 KiB per SM, two tiles in flight while one is consumed).  The page lookup of a tile's 64 keys is done once
 //     (one thread per key) and shared through shared memory.
@@ -25,6 +27,7 @@ namespace gdn {
 
 constexpr int ATT_H = 8, ATT_KV = 2, ATT_D = 256, ATT_GQA = 4;
 constexpr int TK = 64;                          // keys per tile
+constexpr int ATT_WARPS = 8, ATT_THREADS = 256, KPW = TK / ATT_WARPS;      // 8 keys per warp
 constexpr int ROWB = ATT_D * 2;                 // bytes per key row (512)
 constexpr int TILE_BYTES = TK * ROWB;           // 32 KiB
 constexpr int ATT_STAGES = 3;
@@ -45,6 +48,10 @@ __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
 __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t (&r)[4]) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
 }
+__device__ __forceinline__ void mma_bf16_k8(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(b0));
+}
 __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
@@ -54,7 +61,7 @@ __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * RO
 
 __device__ __forceinline__ int n_splits_of(int ctx, int split_keys) { int n = (ctx + split_keys - 1) / split_keys; return n < 1 ? 1 : n; }
 
-__global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a) {
+__global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const AttnArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
@@ -75,7 +82,7 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a)
 
     // ---- append the new rows to the cache (first split only; readers take them from the inputs) ----
     if (split == 0) {
-        for (int i = tid; i < M * 64; i += 128) {
+        for (int i = tid; i < M * 64; i += ATT_THREADS) {
             const int jj = i >> 6, c = i & 31, isv = (i >> 5) & 1;
             const int pos = ctx + jj;
             const int page = table[pos / a.page_size];
@@ -87,7 +94,7 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a)
     }
 
     // ---- Q rows: row r = j*4 + hq  <->  q[(b*M + j), kvh*4 + hq, :]; rows >= 4M are zero ----
-    for (int i = tid; i < 16 * 32; i += 128) {
+    for (int i = tid; i < 16 * 32; i += ATT_THREADS) {
         const int r = i >> 5, c = i & 31, j = r >> 2, hq = r & 3;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (j < M) v = reinterpret_cast<const uint4*>(a.q + (((size_t)b * M + j) * ATT_H + kvh * ATT_GQA + hq) * ATT_D)[c];
@@ -115,8 +122,8 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a)
         const uint32_t dK = sKV + stage * 2 * TILE_BYTES, dV = dK + TILE_BYTES;
         const int c = tid & 31;
 #pragma unroll 4
-        for (int i = 0; i < 16; i++) {
-            const int r = (tid >> 5) + 4 * i;
+        for (int i = 0; i < 8; i++) {
+            const int r = (tid >> 5) + 8 * i;
             const long long off = row_off[stage * TK + r];
             const __nv_bfloat16 *srcK = a.k_pages, *srcV = a.v_pages;
             int bytes = 0;
@@ -151,31 +158,29 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a)
         const bool new_tile = t >= ctx_tiles;
         const int key0 = new_tile ? 0 : k_begin + t * TK;               // position of the tile's first key in its own numbering
         const int limit = new_tile ? M : k_end - key0;                   // keys of the tile that exist
-        if (warp * 16 < limit) {
+        if (warp * KPW < limit) {
             const uint32_t tK = sKV + stage * 2 * TILE_BYTES, tV = tK + TILE_BYTES;
-            float s[2][4];
+            // scores of this warp's 8 keys: two accumulators (even / odd 16-wide slices of the head dim) halve the MMA chain
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int n = 0; n < 2; n++) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
-#pragma unroll
-            for (int ks = 0; ks < 16; ks++) {
-                uint32_t af[4], bfr[4];
-                ldsm_x4(sQ + swz((lane & 7) + 8 * ((lane >> 3) & 1), 2 * ks + (lane >> 4)), af);
-                ldsm_x4(tK + swz(warp * 16 + (lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1)), bfr);
-                mma_bf16(s[0], af, bfr[0], bfr[1]);
-                mma_bf16(s[1], af, bfr[2], bfr[3]);
+            for (int k2 = 0; k2 < 8; k2++) {
+                uint32_t a0[4], a1[4], bfr[4];
+                ldsm_x4(tK + swz(warp * KPW + (lane & 7), 4 * k2 + (lane >> 3)), bfr);
+                ldsm_x4(sQ + swz((lane & 7) + 8 * ((lane >> 3) & 1), 4 * k2 + (lane >> 4)), a0);
+                ldsm_x4(sQ + swz((lane & 7) + 8 * ((lane >> 3) & 1), 4 * k2 + 2 + (lane >> 4)), a1);
+                mma_bf16(s0, a0, bfr[0], bfr[1]);
+                mma_bf16(s1, a1, bfr[2], bfr[3]);
             }
-            // mask + online softmax; thread holds rows g (e = 0,1) and g + 8 (e = 2,3), keys 16*warp + 8n + 2*t4 + (e & 1)
-            float mx[2] = {-INFINITY, -INFINITY};
+            // mask + online softmax; thread holds rows g (e = 0,1) and g + 8 (e = 2,3), keys 8*warp + 2*t4 + (e & 1)
+            float sv[4], mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int n = 0; n < 2; n++)
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const int kk = warp * 16 + 8 * n + 2 * t4 + (e & 1);
-                    const int row = g + 8 * (e >> 1);
-                    const bool ok = new_tile ? (kk < M && kk <= (row >> 2)) : (kk < limit);
-                    s[n][e] = ok ? s[n][e] * sc : -INFINITY;
-                    mx[e >> 1] = fmaxf(mx[e >> 1], s[n][e]);
-                }
+            for (int e = 0; e < 4; e++) {
+                const int kk = warp * KPW + 2 * t4 + (e & 1);
+                const int row = g + 8 * (e >> 1);
+                const bool ok = new_tile ? (kk < M && kk <= (row >> 2)) : (kk < limit);
+                sv[e] = ok ? (s0[e] + s1[e]) * sc : -INFINITY;
+                mx[e >> 1] = fmaxf(mx[e >> 1], sv[e]);
+            }
             float alpha[2];
 #pragma unroll
             for (int h = 0; h < 2; h++) {
@@ -186,37 +191,32 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a)
                 m_run[h] = mn;
                 l_run[h] *= alpha[h];
             }
-            uint32_t pf[4], pl[4];
+            uint32_t pf[2], pl[2];
             {
-                float p[2][4];
+                float p[4];
 #pragma unroll
-                for (int n = 0; n < 2; n++)
-#pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const float mn = m_run[e >> 1];
-                        p[n][e] = (mn == -INFINITY) ? 0.f : exp2f(s[n][e] - mn);
-                        l_run[e >> 1] += p[n][e];
-                    }
-                pf[0] = pack_bf16x2(p[0][0], p[0][1]); pf[1] = pack_bf16x2(p[0][2], p[0][3]);
-                pf[2] = pack_bf16x2(p[1][0], p[1][1]); pf[3] = pack_bf16x2(p[1][2], p[1][3]);
+                for (int e = 0; e < 4; e++) {
+                    const float mn = m_run[e >> 1];
+                    p[e] = (mn == -INFINITY) ? 0.f : exp2f(sv[e] - mn);
+                    l_run[e >> 1] += p[e];
+                }
+                pf[0] = pack_bf16x2(p[0], p[1]); pf[1] = pack_bf16x2(p[2], p[3]);
                 // low parts: p - bf16(p), exact in fp32, then rounded to bf16 (16 significand bits in total)
 #pragma unroll
-                for (int n = 0; n < 2; n++)
-#pragma unroll
-                    for (int e = 0; e < 4; e++) p[n][e] -= bf(p[n][e]);
-                pl[0] = pack_bf16x2(p[0][0], p[0][1]); pl[1] = pack_bf16x2(p[0][2], p[0][3]);
-                pl[2] = pack_bf16x2(p[1][0], p[1][1]); pl[3] = pack_bf16x2(p[1][2], p[1][3]);
+                for (int e = 0; e < 4; e++) p[e] -= bf(p[e]);
+                pl[0] = pack_bf16x2(p[0], p[1]); pl[1] = pack_bf16x2(p[2], p[3]);
             }
 #pragma unroll
             for (int n = 0; n < 32; n++) { o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1]; }
 #pragma unroll
-            for (int nb = 0; nb < 16; nb++) {
+            for (int nq = 0; nq < 8; nq++) {
                 uint32_t vf[4];
-                ldsm_x4_t(tV + swz(warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * nb + (lane >> 4)), vf);
-                mma_bf16(o[2 * nb], pf, vf[0], vf[1]);
-                mma_bf16(o[2 * nb + 1], pf, vf[2], vf[3]);
-                mma_bf16(o[2 * nb], pl, vf[0], vf[1]);
-                mma_bf16(o[2 * nb + 1], pl, vf[2], vf[3]);
+                ldsm_x4_t(tV + swz(warp * KPW + (lane & 7), 4 * nq + (lane >> 3)), vf);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    mma_bf16_k8(o[4 * nq + i], pf[0], pf[1], vf[i]);
+                    mma_bf16_k8(o[4 * nq + i], pl[0], pl[1], vf[i]);
+                }
             }
         }
         // this tile's row offsets were consumed two iterations ago: plan tile t+3 into the same slot; the barrier below orders
@@ -228,8 +228,8 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a)
     __syncthreads();
 
     // ---- merge the four warps (each saw a different quarter of every tile) through shared memory ----
-    float* mO = reinterpret_cast<float*>(smem + 16 * ROWB);              // [4][16][256]
-    float* mML = mO + 4 * 16 * ATT_D;                                    // [4][16][2]
+    float* mO = reinterpret_cast<float*>(smem + 16 * ROWB);              // [8][16][256]
+    float* mML = mO + ATT_WARPS * 16 * ATT_D;                            // [8][16][2]
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
@@ -248,17 +248,17 @@ __global__ void __launch_bounds__(128) gqa_decode_split_kernel(const AttnArgs a)
     __syncthreads();
     float* part = a.part + (((size_t)b * ATT_KV + kvh) * a.max_splits + split) * PART_STRIDE;
     for (int r = 0; r < 4 * M; r++) {
-        float mw[4], mstar = -INFINITY;
+        float mw[ATT_WARPS], mstar = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; w++) { mw[w] = mML[(w * 16 + r) * 2]; mstar = fmaxf(mstar, mw[w]); }
-        float wgt[4], lsum = 0.f;
+        for (int w = 0; w < ATT_WARPS; w++) { mw[w] = mML[(w * 16 + r) * 2]; mstar = fmaxf(mstar, mw[w]); }
+        float wgt[ATT_WARPS], lsum = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; w++) { wgt[w] = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - mstar); lsum += wgt[w] * mML[(w * 16 + r) * 2 + 1]; }
-#pragma unroll
-        for (int d = tid; d < ATT_D; d += 128) {
+        for (int w = 0; w < ATT_WARPS; w++) { wgt[w] = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - mstar); lsum += wgt[w] * mML[(w * 16 + r) * 2 + 1]; }
+        {
+            const int d = tid;                                           // 256 threads = 256 dims
             float acc = 0.f;
 #pragma unroll
-            for (int w = 0; w < 4; w++) acc += wgt[w] * mO[(w * 16 + r) * ATT_D + d];
+            for (int w = 0; w < ATT_WARPS; w++) acc += wgt[w] * mO[(w * 16 + r) * ATT_D + d];
             part[r * ATT_D + d] = acc;
         }
         if (tid == 0) { part[16 * ATT_D + 2 * r] = mstar; part[16 * ATT_D + 2 * r + 1] = lsum; }
@@ -290,9 +290,10 @@ __global__ void __launch_bounds__(128) gqa_decode_merge_kernel(const AttnArgs a)
     o[tid + 128] = __float2bfloat16_rn(acc1 * inv);
 }
 
-// split size (keys) so that a batch of B sequences of up to max_ctx keys gives about 4 blocks per SM
+// split size (keys): a block has a fixed cost (pipeline fill, the merge of its eight warps, its partial) of several tile times, so
+// splits are as long as they can be while a batch of B sequences of up to max_ctx keys still gives about one block per SM
 void gqa_split_plan(int B, int max_ctx, int* split_keys, int* max_splits) {
-    long long sk = (long long)max_ctx * B * ATT_KV / 592;
+    long long sk = (long long)max_ctx * B * ATT_KV / 200;
     sk = (sk / TK) * TK;
     if (sk < 2 * TK) sk = 2 * TK;
     if (sk > 4096) sk = 4096;
@@ -319,7 +320,7 @@ int launch_gqa_decode(AttnArgs a, int max_ctx, cudaStream_t stream) {
             return check_launch("gqa_decode smem attribute");
         attr_set[dev] = true;
     }
-    gqa_decode_split_kernel<<<dim3(a.max_splits, ATT_KV, a.B), 128, ATT_SMEM, stream>>>(a);
+    gqa_decode_split_kernel<<<dim3(a.max_splits, ATT_KV, a.B), ATT_THREADS, ATT_SMEM, stream>>>(a);
     int rc = check_launch("gqa_decode_split");
     if (rc) return rc;
     gqa_decode_merge_kernel<<<dim3(a.B * a.M, ATT_H), 128, 0, stream>>>(a);
