@@ -40,6 +40,10 @@ STATE_BYTES = HV * DV * DK * 4
 # algorithmic bytes of one decode step of one (sequence, layer): state read + state written + mixed-qkv row + conv window read
 # + conv window written + y  (M = 1)
 DECODE_BYTES_PER_SEQ_LAYER = 2 * STATE_BYTES + CD * 2 + 3 * CD * 2 + 3 * CD * 2 + HV * DV * 2
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at B=64 from the ncu capture summarised in
+# profiles/gdn_decode_kernel_B64.md (70.34 MB read + 12.64 MB written; the rest of the 67 MB of state written by a launch is
+# still in L2 when the kernel ends and is written back during the following launches)
+DECODE_TRAFFIC_NCU = 82978816
 PREFILL_FLOP_PER_TOKEN_LAYER = HV * (8 * 64 * 128 + 6 * 128 * 128)        # chunk 64: 2,621,440
 PREFILL_BYTES_PER_TOKEN_LAYER = 4 * HV * 128 * 2 + 2 * HV * 4                # q,k,v,y bf16 + log-decay, beta fp32 = 16,512
 
@@ -418,14 +422,7 @@ def main():
                 e2e=dict(value=n * 1e3 / dec["e2e_ms_per_step"], unit="steps/s", h2d_bytes_per_step=dec["h2d"], d2h_bytes_per_step=dec["d2h"]),
                 roofline=dict(bound="hbm", kernel="gdn_decode_kernel<2>", achieved=dec["achieved_gbs"], peak=peaks["hbm_gbs"], unit="GB/s",
                               frac=dec["frac"], peak_source=peaks["source"], launch_us=dec["launch_us"],
-                              algorithmic_bytes_per_launch=B_DECODE * DECODE_BYTES_PER_SEQ_LAYER, traffic=None))
-    tr = ROOT / "profiles" / "traffic.json"
-    if tr.exists():
-        try:
-            line["roofline"]["traffic"] = json.loads(tr.read_text()).get("gdn_decode_kernel_B64_bytes_per_launch")
-        except (ValueError, OSError):
-            pass
-
+                              algorithmic_bytes_per_launch=B_DECODE * DECODE_BYTES_PER_SEQ_LAYER, traffic=DECODE_TRAFFIC_NCU))
     if rank == 0 and world == 1:
         extra = {}
         if not args.no_extra:
