@@ -136,6 +136,31 @@ int gqa_decode_paged_static(const void* q, const void* k_new, const void* v_new,
                             const int* ctx_len, void* out, int B, int M, int page_size, int max_pages, int n_pages, int max_ctx,
                             void* stream);
 
+/* Glue between the qkv projection of a full-attention layer and gqa_decode_paged: per row, split q | gate per head, k, v;
+ * rms_norm(q, q_norm) and rms_norm(k, k_norm) over 256; RoPE on dims [0, 64) (pairs i, i+32; angle pos * theta^(-i/32)).
+ * Replaces: the MLX calls at qwen35/fast.py:70-78 (= qwen35/batch.py:504-511, qwen35/model.py:148-161).
+ *   qkv bf16 [R, row_stride >= 5120] (8 x (q 256 | gate 256), k 2 x 256, v 2 x 256);  q_norm, k_norm fp32 [256] (the "+1" of
+ *   the checkpoint already folded in, qwen35/model.py:95-96);  row_pos int32 [R] position of every row
+ *   q bf16 [R,8,256], gate bf16 [R,8,256], k, v bf16 [R,2,256] */
+int gqa_qkv_prep(const void* qkv, long long row_stride, const float* q_norm, const float* k_norm, const int* row_pos, void* q, void* gate, void* k,
+                 void* v, int R, float eps, float rope_theta, void* stream);
+
+/* out = o * sigmoid(gate), elementwise over n bf16 values (n % 4 == 0).  Replaces: qwen35/fast.py:84, qwen35/batch.py:512. */
+int gqa_gate_out(const void* o, const void* gate, void* out, long long n, void* stream);
+
+/* Prefill front end of a GDN layer: depthwise causal conv (4 taps) + silu on the mixed qkv columns of proj, q/k l2norm (q also
+ * scaled by 128^-1/2), and the new conv window (last 3 raw rows).
+ * Replaces: conv_prep, qwen35/prefill.py:96-134,160-238; window update qwen35/prefill.py:262-263.
+ *   proj bf16 [S, row_stride >= 8224];  conv_state bf16 [3,6144];  conv_w bf16 [6144*4]
+ *   q, k, v bf16 [S,16,128];  new_conv bf16 [3,6144] (must not alias conv_state) */
+int gdn_conv_prep(const void* proj, long long row_stride, const void* conv_state, const void* conv_w, void* q, void* k, void* v, void* new_conv,
+                  int S, void* stream);
+
+/* Gated RMSNorm on the GDN output: out = silu(z) * w * y * rsqrt(mean(y^2) + 1e-6) per (token, head), z = proj[:, 6144:8192].
+ * Replaces: gated_norm, qwen35/prefill.py:137-157,241-244.
+ *   y bf16 [S,2048];  proj bf16 [S, row_stride >= 8224];  gw fp32 [128];  out bf16 [S,2048] */
+int gdn_gated_norm(const void* y, const void* proj, long long row_stride, const float* gw, void* out, long long S, void* stream);
+
 /* dst.flat[d0 + y*dstride + i] = src.flat[s0 + y*sstride + i] for i < n, y < ny; offsets in elements of elem_size (2 or 4) bytes.
  * Replaces: blit, qwen35/batch.py:349-372. */
 int gdn_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,

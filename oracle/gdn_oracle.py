@@ -244,6 +244,63 @@ def attn_rows(q, k_new, v_new, k_ctx, v_ctx, dtype=np.float64):
     return out
 
 
+def qkv_prep(qkv, q_norm, k_norm, row_pos, eps=1e-6, theta=1e7, rope_dim=64):
+    """Attention glue in front of the decode attention (qwen35/fast.py:70-78, qwen35/model.py:148-161): split a qkv row into
+    8 x (q 256 | gate 256), k 2 x 256, v 2 x 256; rms_norm q and k over 256 with weights; rotate dims [0, 64) of q and k
+    (half-split pairs i, i + 32; angle pos * theta^(-i/32)).  One bf16 rounding after the norm and one after the rotation,
+    as two MLX ops give.  Returns (q [R,8,256], gate [R,2048], k [R,2,256], v [R,2,256]) as bf16-exact fp32."""
+    qkv = np.asarray(qkv, np.float32)
+    R = qkv.shape[0]
+    qg = qkv[:, :4096].reshape(R, 8, 512)
+    q, gate = qg[:, :, :256], qg[:, :, 256:].reshape(R, 2048)
+    k = qkv[:, 4096:4608].reshape(R, 2, 256)
+    v = qkv[:, 4608:5120].reshape(R, 2, 256)
+
+    def norm(x, w):
+        ms = (x.astype(np.float64) ** 2).mean(-1, keepdims=True)
+        return bf16_round((x / np.sqrt(ms + eps) * np.asarray(w, np.float64)).astype(np.float32))
+
+    def rope(x):
+        half = rope_dim // 2
+        ang = np.asarray(row_pos, np.float64)[:, None, None] * theta ** (-np.arange(half) / half)[None, None, :]
+        x1, x2 = x[..., :half].astype(np.float64), x[..., half:rope_dim].astype(np.float64)
+        out = x.copy()
+        out[..., :half] = bf16_round((x1 * np.cos(ang) - x2 * np.sin(ang)).astype(np.float32))
+        out[..., half:rope_dim] = bf16_round((x1 * np.sin(ang) + x2 * np.cos(ang)).astype(np.float32))
+        return out
+    return rope(norm(q, q_norm)), gate.copy(), rope(norm(k, k_norm)), v.copy()
+
+
+def gate_out(o, gate):
+    """o * sigmoid(gate) on bf16 arrays (qwen35/fast.py:84): sigmoid evaluated op by op in bf16, product rounded."""
+    return bf16_round(np.asarray(o, np.float32) * sigmoid_bf16(gate))
+
+
+def conv_prep(proj, conv_state, conv_w):
+    """Prefill conv + silu + q/k l2norm over S tokens (qwen35/prefill.py:96-134,160-238) and the new window (:262-263).
+    proj [S, 8224], conv_state [3, 6144], conv_w [6144*4].  Returns (q, k, v [S,16,128], new_conv [3,6144])."""
+    proj = np.asarray(proj, np.float32)
+    S = proj.shape[0]
+    w = np.asarray(conv_w, np.float32).reshape(CD, 4)
+    rows = np.concatenate([np.asarray(conv_state, np.float32).reshape(3, CD), proj[:, :CD]], axis=0)
+    acc = rows[0:S] * w[:, 0]
+    acc = acc + rows[1:S + 1] * w[:, 1]
+    acc = acc + rows[2:S + 2] * w[:, 2]
+    acc = acc + rows[3:S + 3] * w[:, 3]
+    c = silu_bf16(bf16_round(acc))
+    q, k = normalize_qk(c[:, :KD].reshape(S, HV, DK), c[:, KD:2 * KD].reshape(S, HV, DK))
+    return q, k, c[:, 2 * KD:].reshape(S, HV, DV), rows[S:S + 3].copy()
+
+
+def gated_norm(y, proj, gw):
+    """silu(z) * gw * y * rsqrt(mean(y^2) + 1e-6) per (token, head), one rounding at the end (qwen35/prefill.py:137-157)."""
+    y = np.asarray(y, np.float64).reshape(-1, HV, DV)
+    z = np.asarray(proj, np.float64)[:, CD:CD + HV * DV].reshape(-1, HV, DV)
+    inv = 1.0 / np.sqrt((y ** 2).mean(-1, keepdims=True) + 1e-6)
+    out = z / (1.0 + np.exp(-z)) * (np.asarray(gw, np.float64)[None, None, :] * (y * inv))
+    return bf16_round(out.astype(np.float32)).reshape(-1, HV * DV)
+
+
 # ---------------------------------------------------------------------------------------------------------------------
 # speculative acceptance (integer work: bit-exact contract)
 # ---------------------------------------------------------------------------------------------------------------------

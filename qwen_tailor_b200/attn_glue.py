@@ -1,0 +1,35 @@
+"""The glue around the decode attention of a full-attention layer (the MLX library calls of the reference's
+``qwen35/fast.py:70-85`` / ``qwen35/batch.py:504-513``) as two CUDA kernels."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import check, ptr, stream_ptr
+from .gated_delta import _f32
+
+
+def qkv_prep(qkv, q_norm, k_norm, row_pos, eps=1e-6, rope_theta=1e7):
+    """qkv [R, 5120] bf16 (8 x (q | gate), k, v) -> q [R,8,256], gate [R,2048], k [R,2,256], v [R,2,256]: q and k are
+    rms-normed with q_norm / k_norm and rotated (first 64 dims, half-split pairs) at positions row_pos (int32 [R])."""
+    _lib.require_cuda(qkv, q_norm, k_norm, row_pos)
+    assert qkv.dtype == torch.bfloat16 and qkv.dim() == 2 and qkv.shape[1] >= 5120 and qkv.stride(1) == 1 and row_pos.dtype == torch.int32
+    R = qkv.shape[0]
+    dev = qkv.device
+    q = torch.empty((R, 8, 256), dtype=torch.bfloat16, device=dev)
+    gate = torch.empty((R, 8, 256), dtype=torch.bfloat16, device=dev)
+    k = torch.empty((R, 2, 256), dtype=torch.bfloat16, device=dev)
+    v = torch.empty((R, 2, 256), dtype=torch.bfloat16, device=dev)
+    check(_lib.load().gqa_qkv_prep(ptr(qkv), qkv.stride(0), ptr(_f32(q_norm)), ptr(_f32(k_norm)), ptr(row_pos), ptr(q), ptr(gate), ptr(k), ptr(v), R,
+                                   float(eps), float(rope_theta), stream_ptr(dev)), "qkv_prep")
+    return q, gate.view(R, 2048), k, v
+
+
+def gate_out(o, gate):
+    """o * sigmoid(gate) with the bf16 rounding points of the unfused graph; o [R,8,256] or [R,2048], gate [R,2048]."""
+    _lib.require_cuda(o, gate)
+    o2 = o.reshape(o.shape[0], -1).contiguous()
+    g2 = gate.reshape(o2.shape).contiguous()
+    out = torch.empty_like(o2)
+    check(_lib.load().gqa_gate_out(ptr(o2), ptr(g2), ptr(out), o2.numel(), stream_ptr(o.device)), "gate_out")
+    return out

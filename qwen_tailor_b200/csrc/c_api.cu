@@ -208,6 +208,38 @@ int gqa_decode_paged_static(const void* q, const void* k_new, const void* v_new,
     return launch_gqa_decode_static(a, max_ctx, static_cast<cudaStream_t>(stream));
 }
 
+int gqa_qkv_prep(const void* qkv, long long row_stride, const float* q_norm, const float* k_norm, const int* row_pos, void* q, void* gate, void* k,
+                 void* v, int R, float eps, float rope_theta, void* stream) {
+    REQUIRE(qkv && q_norm && k_norm && row_pos && q && gate && k && v, GDN_E_NULL, "gqa_qkv_prep: null pointer");
+    REQUIRE(R >= 0 && row_stride >= 5120 && rope_theta > 1.f, GDN_E_SHAPE, "gqa_qkv_prep: R=%d row_stride=%lld theta=%g", R, row_stride, rope_theta);
+    typedef const __nv_bfloat16* cb; typedef __nv_bfloat16* b;
+    return launch_qkv_prep((cb)qkv, row_stride, q_norm, k_norm, row_pos, (b)q, (b)gate, (b)k, (b)v, R, eps, rope_theta, static_cast<cudaStream_t>(stream));
+}
+
+int gqa_gate_out(const void* o, const void* gate, void* out, long long n, void* stream) {
+    REQUIRE(o && gate && out, GDN_E_NULL, "gqa_gate_out: null pointer");
+    REQUIRE(n >= 0 && n % 4 == 0, GDN_E_SHAPE, "gqa_gate_out: n=%lld must be a multiple of 4", n);
+    REQUIRE(((uintptr_t)o | (uintptr_t)gate | (uintptr_t)out) % 8 == 0, GDN_E_ALIGN, "gqa_gate_out: tensors must be 8-byte aligned");
+    return launch_gate_out((const __nv_bfloat16*)o, (const __nv_bfloat16*)gate, (__nv_bfloat16*)out, n, static_cast<cudaStream_t>(stream));
+}
+
+int gdn_conv_prep(const void* proj, long long row_stride, const void* conv_state, const void* conv_w, void* q, void* k, void* v, void* new_conv,
+                  int S, void* stream) {
+    REQUIRE(proj && conv_state && conv_w && q && k && v && new_conv, GDN_E_NULL, "gdn_conv_prep: null pointer");
+    REQUIRE(S >= 0 && row_stride >= PW && row_stride % 4 == 0, GDN_E_SHAPE, "gdn_conv_prep: S=%d row_stride=%lld", S, row_stride);
+    REQUIRE(((uintptr_t)proj | (uintptr_t)conv_state | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)new_conv) % 8 == 0, GDN_E_ALIGN,
+            "gdn_conv_prep: tensors must be 8-byte aligned");
+    typedef const __nv_bfloat16* cb; typedef __nv_bfloat16* b;
+    return launch_conv_prep((cb)proj, row_stride, (cb)conv_state, (cb)conv_w, (b)q, (b)k, (b)v, (b)new_conv, S, static_cast<cudaStream_t>(stream));
+}
+
+int gdn_gated_norm(const void* y, const void* proj, long long row_stride, const float* gw, void* out, long long S, void* stream) {
+    REQUIRE(y && proj && gw && out, GDN_E_NULL, "gdn_gated_norm: null pointer");
+    REQUIRE(S >= 0 && row_stride >= PW && row_stride % 4 == 0, GDN_E_SHAPE, "gdn_gated_norm: S=%lld row_stride=%lld", S, row_stride);
+    REQUIRE(((uintptr_t)y | (uintptr_t)proj | (uintptr_t)out) % 8 == 0, GDN_E_ALIGN, "gdn_gated_norm: tensors must be 8-byte aligned");
+    return launch_gated_norm((const __nv_bfloat16*)y, (const __nv_bfloat16*)proj, row_stride, gw, (__nv_bfloat16*)out, S, static_cast<cudaStream_t>(stream));
+}
+
 int gdn_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,
                    long long sstride, void* stream) {
     REQUIRE(dst && src, GDN_E_NULL, "gdn_state_copy: null pointer");

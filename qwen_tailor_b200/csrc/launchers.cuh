@@ -73,6 +73,15 @@ struct PrefillArgs {
 };
 int launch_prefill(const void* q, const void* k, const void* v, const PrefillArgs& a, cudaStream_t stream);
 
+// ---- attn_glue.cu ----
+int launch_qkv_prep(const __nv_bfloat16* qkv, long long row_stride, const float* q_norm, const float* k_norm, const int* row_pos, __nv_bfloat16* q,
+                    __nv_bfloat16* gate, __nv_bfloat16* k, __nv_bfloat16* v, int R, float eps, float theta, cudaStream_t st);
+int launch_gate_out(const __nv_bfloat16* o, const __nv_bfloat16* gate, __nv_bfloat16* out, long long n, cudaStream_t st);
+int launch_conv_prep(const __nv_bfloat16* proj, long long row_stride, const __nv_bfloat16* conv_state, const __nv_bfloat16* conv_w, __nv_bfloat16* q,
+                     __nv_bfloat16* k, __nv_bfloat16* v, __nv_bfloat16* new_conv, int S, cudaStream_t st);
+int launch_gated_norm(const __nv_bfloat16* y, const __nv_bfloat16* proj, long long row_stride, const float* gw, __nv_bfloat16* out, long long S,
+                      cudaStream_t st);
+
 // ---- state_copy.cu ----
 int launch_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,
                       long long sstride, cudaStream_t st);
