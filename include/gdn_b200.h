@@ -114,8 +114,9 @@ size_t gqa_decode_workspace_bytes(int B, int max_ctx);
  * page_size = Lmax, max_pages = 1, block_table = slots.
  *   q bf16 [B*M,8,256] (normed + roped, unscaled);  k_new, v_new bf16 [B*M,2,256]
  *   k_pages, v_pages bf16 [n_pages,2,page_size,256];  block_table int32 [B,max_pages];  ctx_len int32 [B] (tokens cached)
- *   out bf16 [B*M,8,256];  workspace: gqa_decode_workspace_bytes(B, max_ctx) bytes, 16-byte aligned
- *   max_ctx: host-side upper bound of ctx_len (sizes the split-KV grid) */
+ *   out bf16 [B*M,8,256];  workspace: gqa_decode_workspace_bytes(B, max_ctx) bytes, 16-byte aligned (a smaller one is served
+ *   with fewer blocks as long as it holds the plan and 2 B + 1 partials)
+ *   max_ctx: host-side upper bound of ctx_len (informational: the work split is derived from ctx_len on the device) */
 int gqa_decode_paged(const void* q, const void* k_new, const void* v_new, void* k_pages, void* v_pages, const int* block_table,
                      const int* ctx_len, void* out, void* workspace, size_t workspace_bytes, int B, int M, int page_size,
                      int max_pages, int n_pages, int max_ctx, void* stream);
@@ -124,10 +125,11 @@ int gqa_decode_paged(const void* q, const void* k_new, const void* v_new, void* 
  * plugged into a serving runtime that reserved the whole device up front and forbids allocation calls on its request path, or
  * a plain C caller that has no allocator of its own to size a workspace with.  This entry point has no counterpart in the
  * reference; it exists only for such hosts.  Same arguments and results as gqa_decode_paged, minus the workspace: the
- * split-KV partials go to a 12 MiB array built into the library (held by every GPU that loads the library until the process
+ * work plan and the split-KV partials go to a 12 MiB array built into the library (held by every GPU that loads the library until the process
  * exits).  Nothing is allocated or freed, here or in anything it calls.
- *   Limit: B * 2 * ceil(max_ctx / split) partials must fit the array (762 of them; e.g. B = 16 at max_ctx = 8192 needs 224).
- *          Larger problems return GDN_E_SHAPE with a message that names the limit; use gqa_decode_paged for them.
+ *   Limit: at most 256 sequences per call (the array holds the work plan and 762 partials: one per SM plus one per
+ *          (sequence, kv head) pair).  Larger batches return GDN_E_SHAPE with a message that names the limit; use
+ *          gqa_decode_paged for them.
  *   First call on a device: looks up the array's device address (cudaGetSymbolAddress, with that device current).  Make that
  *          first call outside any stream capture.
  *   Sharing: all calls on a device use the same array, which keeps the previous call's contents.  Nothing in it needs

@@ -65,7 +65,7 @@ def attn_paged_static(q, k_new, v_new, k_pages, v_pages, block_table, ctx_len, M
     """``attn_paged`` without any allocation on the way to the kernel except the output tensor: the split-KV partials go to a
     12 MiB scratch array built into the library instead of a torch workspace.  Meant for hosts that may not allocate device
     memory while serving (their C callers pass a preallocated output and use the C entry point ``gqa_decode_paged_static``
-    directly).  Raises ValueError when the batch needs more than the 762 partials the array holds.  Calls that overlap on one
+    directly).  Raises ValueError for more than 256 sequences per call (what the array is sized for).  Calls that overlap on one
     GPU share the array and must not run concurrently; the first call on a device should happen outside stream capture."""
     _lib.require_cuda(q, k_new, v_new, k_pages, v_pages, block_table, ctx_len)
     R, H, D = q.shape

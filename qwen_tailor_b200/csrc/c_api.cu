@@ -183,11 +183,11 @@ int gqa_decode_paged(const void* q, const void* k_new, const void* v_new, void* 
     AttnArgs a{};
     a.q = static_cast<const __nv_bfloat16*>(q); a.k_new = static_cast<const __nv_bfloat16*>(k_new); a.v_new = static_cast<const __nv_bfloat16*>(v_new);
     a.k_pages = static_cast<__nv_bfloat16*>(k_pages); a.v_pages = static_cast<__nv_bfloat16*>(v_pages);
-    a.block_table = block_table; a.ctx_len = ctx_len; a.out = static_cast<__nv_bfloat16*>(out); a.part = static_cast<float*>(workspace);
+    a.block_table = block_table; a.ctx_len = ctx_len; a.out = static_cast<__nv_bfloat16*>(out);
     a.B = B; a.M = M; a.page_size = page_size; a.max_pages = max_pages; a.n_pages = n_pages;
     a.status = status_ptr();
     REQUIRE(a.status, GDN_E_LAUNCH, "gqa_decode_paged: no CUDA device");
-    return launch_gqa_decode(a, max_ctx, static_cast<cudaStream_t>(stream));
+    return launch_gqa_decode(a, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int gqa_decode_paged_static(const void* q, const void* k_new, const void* v_new, void* k_pages, void* v_pages, const int* block_table,
@@ -205,7 +205,7 @@ int gqa_decode_paged_static(const void* q, const void* k_new, const void* v_new,
     a.B = B; a.M = M; a.page_size = page_size; a.max_pages = max_pages; a.n_pages = n_pages;
     a.status = status_ptr();
     REQUIRE(a.status, GDN_E_LAUNCH, "gqa_decode_paged_static: no CUDA device");
-    return launch_gqa_decode_static(a, max_ctx, static_cast<cudaStream_t>(stream));
+    return launch_gqa_decode_static(a, static_cast<cudaStream_t>(stream));
 }
 
 int gqa_qkv_prep(const void* qkv, long long row_stride, const float* q_norm, const float* k_norm, const int* row_pos, void* q, void* gate, void* k,

@@ -7,14 +7,16 @@
 // page_size = Lmax, block_table[b] = {slot}.
 //
 // The kernel is bound by streaming K and V once (2 KiB per cached token and layer).  Design:
-//   * split-KV: grid (split, kv_head, sequence); every block streams `split_keys` keys of one (sequence, kv head) so that a
-//     ragged batch still fills 148 SMs; partial (max, sum, O) go to a caller-provided fp32 workspace and a second kernel
-//     merges them.
+//   * balanced split-KV: the 64-key tiles of all (sequence, kv head) pairs form one list (a tiny plan kernel builds its prefix
+//     sums from ctx_len on the device), and one persistent block per SM takes a contiguous 1/n-th of it, so a ragged batch
+//     loads every SM equally whatever the context lengths are.  Where a block's range crosses from one pair to the next, or
+//     ends inside one, it writes a partial (max, sum, O) to a caller-provided fp32 workspace; a merge kernel combines the
+//     1..few partials of each pair.
 //   * GQA packing: the 4 query heads of a KV head times the M <= 4 chained rows form the 16 rows of a warp-level
 //     m16n8k16 bf16 MMA, so each K/V byte is read once for up to 16 query rows (at M = 4 plain FMAs could not keep up with
-//     HBM).  Each of the 8 warps owns 8 of the 64 keys of a tile (scores by m16n8k16, P.V by m16n8k8) and keeps its own
-//     online-softmax state; eight warps rather than four because the per-tile dependency chains (16 chained score MMAs,
-//     the softmax shuffles) are latency-bound and need other warps to hide behind.
+//     HBM).  The 8 warps are 4 key groups x 2 halves of the head dim: a warp computes the scores of its 16 keys of a tile
+//     (both warps of a pair do, it is cheap) and P.V for its 128 of the 256 dims, with its own online-softmax state; eight
+//     warps rather than four because the per-tile dependency chains are latency-bound and need other warps to hide behind.
 //   * K/V tiles (64 keys x 512 B) are gathered page by page with 16-byte cp.async into XOR-swizzled shared memory, three
 //     stages (192 KiB per SM, two tiles in flight while one is consumed).  The page lookup of a tile's 64 keys is done once
 //     (one thread per key) and shared through shared memory.
@@ -27,7 +29,7 @@ namespace gdn {
 
 constexpr int ATT_H = 8, ATT_KV = 2, ATT_D = 256, ATT_GQA = 4;
 constexpr int TK = 64;                          // keys per tile
-constexpr int ATT_WARPS = 8, ATT_THREADS = 256, KPW = TK / ATT_WARPS;      // 8 keys per warp
+constexpr int ATT_THREADS = 256, KGROUPS = 4, KPW = TK / KGROUPS;      // 4 key groups of 16 keys x 2 dim halves
 constexpr int ROWB = ATT_D * 2;                 // bytes per key row (512)
 constexpr int TILE_BYTES = TK * ROWB;           // 32 KiB
 constexpr int ATT_STAGES = 3;
@@ -59,22 +61,101 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 // byte offset of 16-byte chunk `c` of row `r` in a swizzled [rows][512 B] tile
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * ROWB + ((c ^ (r & 7)) << 4)); }
 
-__device__ __forceinline__ int n_splits_of(int ctx, int split_keys) { int n = (ctx + split_keys - 1) / split_keys; return n < 1 ? 1 : n; }
+// ---- work plan in the workspace: ints meta[0] = total tiles, meta[1] = working blocks, then cum[P+1] (tile prefix sums per (sequence, kv head) pair),
+//      base[P+1] (partial-slot prefix sums), first[P] (first block of each pair), count[P] (arrival counters, zeroed by the plan
+//      kernel of every call); the fp32 partials follow ----
+__host__ __device__ __forceinline__ size_t meta_ints(int P) { return ((size_t)(4 + 4 * (P + 1)) + 63) / 64 * 64; }
+__device__ __forceinline__ int* meta_cum(int* meta) { return meta + 4; }
+__device__ __forceinline__ int* meta_base(int* meta, int P) { return meta + 4 + (P + 1); }
+__device__ __forceinline__ int* meta_first(int* meta, int P) { return meta + 4 + 2 * (P + 1); }
+__device__ __forceinline__ int* meta_count(int* meta, int P) { return meta + 4 + 3 * (P + 1); }     // partials written so far, per pair
+// block that owns tile i when G blocks split N tiles as [c N / G, (c + 1) N / G)
+__device__ __forceinline__ int block_of_tile(long long i, int G, long long N) { return (int)(((i + 1) * G - 1) / N); }
+
+__global__ void __launch_bounds__(256) gqa_decode_plan_kernel(const AttnArgs a) {
+    __shared__ int s_sum[256];
+    const int tid = threadIdx.x, P = a.P;
+    int* cum = meta_cum(a.meta);
+    int* base = meta_base(a.meta, P);
+    int* first = meta_first(a.meta, P);
+    const int chunk = (P + 255) / 256, p0 = min(P, tid * chunk), p1 = min(P, p0 + chunk);
+    auto tiles_of = [&](int p) -> int {
+        const int ctx = a.ctx_len[p / ATT_KV];
+        if (ctx < 0 || (long long)ctx + a.M > (long long)a.max_pages * a.page_size) { atomicExch(a.status, 1); return 0; }
+        return (ctx + TK - 1) / TK + 1;                               // cached keys + one tile for the rows of this call
+    };
+    auto scan = [&](int local) -> int {                               // exclusive prefix of `local` over the block
+        int x = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, x, o); if ((tid & 31) >= o) x += y; }
+        __syncthreads();
+        if ((tid & 31) == 31) s_sum[tid >> 5] = x;
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < (tid >> 5); w++) before += s_sum[w];
+        return before + x - local;
+    };
+    int local = 0;
+    for (int p = p0; p < p1; p++) local += tiles_of(p);
+    int run = scan(local);
+    for (int p = p0; p < p1; p++) { cum[p] = run; run += tiles_of(p); }
+    if (p1 == P && p0 <= P && tid == min(255, (P - 1) / max(chunk, 1))) { cum[P] = run; a.meta[0] = run; }
+    __syncthreads();
+    __threadfence_block();
+    const long long N = cum[P];
+    // with fewer tiles than blocks only the first N blocks work (one tile each): every working block then has a non-empty range,
+    // so the blocks of a pair are consecutive and each of its partial slots is written
+    const int G = (int)min((long long)a.G, max(N, 1ll));
+    if (tid == 0) a.meta[1] = G;
+    local = 0;
+    for (int p = p0; p < p1; p++) {
+        const int t = cum[p + 1] - cum[p];
+        local += t > 0 ? block_of_tile(cum[p + 1] - 1, G, N) - block_of_tile(cum[p], G, N) + 1 : 0;
+    }
+    run = scan(local);
+    for (int p = p0; p < p1; p++) {
+        const int t = cum[p + 1] - cum[p];
+        const int f = t > 0 ? block_of_tile(cum[p], G, N) : 0;
+        first[p] = f;
+        base[p] = run;
+        run += t > 0 ? block_of_tile(cum[p + 1] - 1, G, N) - f + 1 : 0;
+    }
+    if (tid == min(255, (P - 1) / max(chunk, 1))) base[P] = run;
+    int* count = meta_count(a.meta, P);
+    for (int p = tid; p < P; p += 256) count[p] = 0;
+}
 
 __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const AttnArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
-    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const int M = a.M;
+    const int M = a.M, P = a.P;
+    const int* cum = meta_cum(a.meta);
+    const long long N = a.meta[0];
+    const int G = a.meta[1];                                         // working blocks = min(grid, tiles)
+    if ((int)blockIdx.x >= G) return;
+    long long lo = (long long)blockIdx.x * N / G;
+    const long long hi = (long long)(blockIdx.x + 1) * N / G;
+    if (lo >= hi) return;
+    int pair;                                                        // pair that owns tile lo: cum[pair] <= lo < cum[pair + 1]
+    {
+        int l = 0, r = P - 1;
+        while (l < r) { const int m = (l + r + 1) >> 1; if (cum[m] <= lo) l = m; else r = m - 1; }
+        pair = l;
+    }
+  for (; lo < hi; pair++) {
+    if (cum[pair + 1] <= lo) continue;                               // pairs without tiles (rejected sequences)
+    const long long seg_end = min(hi, (long long)cum[pair + 1]);
+    const int ta = (int)(lo - cum[pair]), tb = (int)(seg_end - cum[pair]);      // this block's tiles of the pair: [ta, tb)
+    const int slot = meta_base(a.meta, P)[pair] + ((int)blockIdx.x - meta_first(a.meta, P)[pair]);
+    lo = seg_end;
+    const int b = pair / ATT_KV, kvh = pair % ATT_KV;
     const int ctx = a.ctx_len[b];
-    if (ctx < 0 || (long long)ctx + M > (long long)a.max_pages * a.page_size) { if (tid == 0) atomicExch(a.status, 1); return; }
-    const int nsp = n_splits_of(ctx, a.split_keys);
-    if (split >= nsp) return;
-    const int k_begin = split * a.split_keys;
-    const int k_end = min(ctx, k_begin + a.split_keys);
-    const bool last = split == nsp - 1;
-    const int ctx_tiles = (k_end - k_begin + TK - 1) / TK;
-    const int ntiles = ctx_tiles + (last ? 1 : 0);
+    const int all_ctx_tiles = (ctx + TK - 1) / TK;                   // tile index all_ctx_tiles holds the rows of this call
+    const int ctx_tiles = max(0, min(tb, all_ctx_tiles) - ta);
+    const int ntiles = tb - ta;
+    const int k_begin = ta * TK;
+    const int k_end = min(ctx, (ta + ctx_tiles) * TK);
+    const int split = ta;                                            // (first block of the pair appends the new rows)
 
     const uint32_t sQ = smem_u32(smem);
     const uint32_t sKV = sQ + 16 * ROWB;
@@ -119,9 +200,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
         }
     };
     auto load_tile = [&](int stage) {
-        const uint32_t dK = sKV + stage * 2 * TILE_BYTES, dV = dK + TILE_BYTES;
         const int c = tid & 31;
-#pragma unroll 4
+        // rows warp, warp + 8, ...: r & 7 is the same for all of them, so the swizzled chunk offset is a per-thread constant
+        const uint32_t dK = sKV + stage * 2 * TILE_BYTES + swz(tid >> 5, c), dV = dK + TILE_BYTES;
+#pragma unroll
         for (int i = 0; i < 8; i++) {
             const int r = (tid >> 5) + 8 * i;
             const long long off = row_off[stage * TK + r];
@@ -129,14 +211,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
             int bytes = 0;
             if (off >= 0) { srcK = a.k_pages + off; srcV = a.v_pages + off; bytes = 16; }
             else if (off <= -2) { srcK = a.k_new + (-2 - off); srcV = a.v_new + (-2 - off); bytes = 16; }
-            cp_async16(dK + swz(r, c), reinterpret_cast<const uint4*>(srcK) + (bytes ? c : 0), bytes);
-            cp_async16(dV + swz(r, c), reinterpret_cast<const uint4*>(srcV) + (bytes ? c : 0), bytes);
+            cp_async16(dK + i * 8 * ROWB, reinterpret_cast<const uint4*>(srcK) + (bytes ? c : 0), bytes);
+            cp_async16(dV + i * 8 * ROWB, reinterpret_cast<const uint4*>(srcV) + (bytes ? c : 0), bytes);
         }
     };
 
-    float o[32][4];
+    const int kg = warp & 3, dh = warp >> 2;                 // key group (16 keys of a tile) and half of the head dim of this warp
+    float o[16][4];
 #pragma unroll
-    for (int n = 0; n < 32; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    for (int n = 0; n < 16; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const float sc = 0.0625f * 1.4426950408889634f;          // 256^-1/2 (qwen35/batch.py:176), scores kept in log2 units
 
@@ -158,29 +241,35 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
         const bool new_tile = t >= ctx_tiles;
         const int key0 = new_tile ? 0 : k_begin + t * TK;               // position of the tile's first key in its own numbering
         const int limit = new_tile ? M : k_end - key0;                   // keys of the tile that exist
-        if (warp * KPW < limit) {
+#ifdef ATT_EXPERIMENT_NO_COMPUTE
+        if (kg * KPW < limit && t < 0) {
+#else
+        if (kg * KPW < limit) {
+#endif
             const uint32_t tK = sKV + stage * 2 * TILE_BYTES, tV = tK + TILE_BYTES;
-            // scores of this warp's 8 keys: two accumulators (even / odd 16-wide slices of the head dim) halve the MMA chain
-            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+            float sc2[2][4];
 #pragma unroll
-            for (int k2 = 0; k2 < 8; k2++) {
-                uint32_t a0[4], a1[4], bfr[4];
-                ldsm_x4(tK + swz(warp * KPW + (lane & 7), 4 * k2 + (lane >> 3)), bfr);
-                ldsm_x4(sQ + swz((lane & 7) + 8 * ((lane >> 3) & 1), 4 * k2 + (lane >> 4)), a0);
-                ldsm_x4(sQ + swz((lane & 7) + 8 * ((lane >> 3) & 1), 4 * k2 + 2 + (lane >> 4)), a1);
-                mma_bf16(s0, a0, bfr[0], bfr[1]);
-                mma_bf16(s1, a1, bfr[2], bfr[3]);
-            }
-            // mask + online softmax; thread holds rows g (e = 0,1) and g + 8 (e = 2,3), keys 8*warp + 2*t4 + (e & 1)
-            float sv[4], mx[2] = {-INFINITY, -INFINITY};
+            for (int n = 0; n < 2; n++) { sc2[n][0] = sc2[n][1] = sc2[n][2] = sc2[n][3] = 0.f; }
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int kk = warp * KPW + 2 * t4 + (e & 1);
-                const int row = g + 8 * (e >> 1);
-                const bool ok = new_tile ? (kk < M && kk <= (row >> 2)) : (kk < limit);
-                sv[e] = ok ? (s0[e] + s1[e]) * sc : -INFINITY;
-                mx[e >> 1] = fmaxf(mx[e >> 1], sv[e]);
+            for (int ks = 0; ks < 16; ks++) {
+                uint32_t af[4], bfr[4];
+                ldsm_x4(sQ + swz((lane & 7) + 8 * ((lane >> 3) & 1), 2 * ks + (lane >> 4)), af);
+                ldsm_x4(tK + swz(kg * KPW + (lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1)), bfr);
+                mma_bf16(sc2[0], af, bfr[0], bfr[1]);
+                mma_bf16(sc2[1], af, bfr[2], bfr[3]);
             }
+            // mask + online softmax; thread holds rows g (e = 0,1) and g + 8 (e = 2,3), keys 16*kg + 8n + 2*t4 + (e & 1)
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < 2; n++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int kk = kg * KPW + 8 * n + 2 * t4 + (e & 1);
+                    const int row = g + 8 * (e >> 1);
+                    const bool ok = new_tile ? (kk < M && kk <= (row >> 2)) : (kk < limit);
+                    sc2[n][e] = ok ? sc2[n][e] * sc : -INFINITY;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], sc2[n][e]);
+                }
             float alpha[2];
 #pragma unroll
             for (int h = 0; h < 2; h++) {
@@ -191,32 +280,42 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
                 m_run[h] = mn;
                 l_run[h] *= alpha[h];
             }
-            uint32_t pf[2], pl[2];
+            uint32_t pf[4], pl[4];
             {
-                float p[4];
+                float p[2][4];
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const float mn = m_run[e >> 1];
-                    p[e] = (mn == -INFINITY) ? 0.f : exp2f(sv[e] - mn);
-                    l_run[e >> 1] += p[e];
-                }
-                pf[0] = pack_bf16x2(p[0], p[1]); pf[1] = pack_bf16x2(p[2], p[3]);
+                for (int n = 0; n < 2; n++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float mn = m_run[e >> 1];
+                        p[n][e] = (mn == -INFINITY) ? 0.f : exp2f(sc2[n][e] - mn);
+                        l_run[e >> 1] += p[n][e];
+                    }
+                pf[0] = pack_bf16x2(p[0][0], p[0][1]); pf[1] = pack_bf16x2(p[0][2], p[0][3]);
+                pf[2] = pack_bf16x2(p[1][0], p[1][1]); pf[3] = pack_bf16x2(p[1][2], p[1][3]);
                 // low parts: p - bf16(p), exact in fp32, then rounded to bf16 (16 significand bits in total)
 #pragma unroll
-                for (int e = 0; e < 4; e++) p[e] -= bf(p[e]);
-                pl[0] = pack_bf16x2(p[0], p[1]); pl[1] = pack_bf16x2(p[2], p[3]);
+                for (int n = 0; n < 2; n++)
+#pragma unroll
+                    for (int e = 0; e < 4; e++) p[n][e] -= bf(p[n][e]);
+                pl[0] = pack_bf16x2(p[0][0], p[0][1]); pl[1] = pack_bf16x2(p[0][2], p[0][3]);
+                pl[2] = pack_bf16x2(p[1][0], p[1][1]); pl[3] = pack_bf16x2(p[1][2], p[1][3]);
+            }
+            // the running maximum rarely moves after the first tiles: skip the rescale of the accumulators when no lane needs it
+            if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+                for (int n = 0; n < 16; n++) { o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1]; }
             }
 #pragma unroll
-            for (int n = 0; n < 32; n++) { o[n][0] *= alpha[0]; o[n][1] *= alpha[0]; o[n][2] *= alpha[1]; o[n][3] *= alpha[1]; }
-#pragma unroll
-            for (int nq = 0; nq < 8; nq++) {
+            for (int nb = 0; nb < 8; nb++) {
                 uint32_t vf[4];
-                ldsm_x4_t(tV + swz(warp * KPW + (lane & 7), 4 * nq + (lane >> 3)), vf);
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    mma_bf16_k8(o[4 * nq + i], pf[0], pf[1], vf[i]);
-                    mma_bf16_k8(o[4 * nq + i], pl[0], pl[1], vf[i]);
-                }
+                ldsm_x4_t(tV + swz(kg * KPW + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * (8 * dh + nb) + (lane >> 4)), vf);
+                mma_bf16(o[2 * nb], pf, vf[0], vf[1]);
+                mma_bf16(o[2 * nb + 1], pf, vf[2], vf[3]);
+#ifndef ATT_EXPERIMENT_NO_LO
+                mma_bf16(o[2 * nb], pl, vf[0], vf[1]);
+                mma_bf16(o[2 * nb + 1], pl, vf[2], vf[3]);
+#endif
             }
         }
         // this tile's row offsets were consumed two iterations ago: plan tile t+3 into the same slot; the barrier below orders
@@ -227,126 +326,161 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
     cp_async_wait<0>();
     __syncthreads();
 
-    // ---- merge the four warps (each saw a different quarter of every tile) through shared memory ----
-    float* mO = reinterpret_cast<float*>(smem + 16 * ROWB);              // [8][16][256]
-    float* mML = mO + ATT_WARPS * 16 * ATT_D;                            // [8][16][2]
+    // ---- merge the four key groups (each saw a different quarter of every tile) through shared memory ----
+    float* mO = reinterpret_cast<float*>(smem + 16 * ROWB);              // [4][16][256]
+    float* mML = mO + KGROUPS * 16 * ATT_D;                              // [4][16][2]
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
     }
 #pragma unroll
-    for (int n = 0; n < 32; n++) {
-        float* p0 = mO + ((warp * 16 + g) * ATT_D) + 8 * n + 2 * t4;
-        p0[0] = o[n][0]; p0[1] = o[n][1];
-        p0[8 * ATT_D] = o[n][2]; p0[8 * ATT_D + 1] = o[n][3];
+    for (int n = 0; n < 16; n++) {
+        float* p0 = mO + ((kg * 16 + g) * ATT_D) + 128 * dh + 8 * n + 2 * t4;
+        *reinterpret_cast<float2*>(p0) = make_float2(o[n][0], o[n][1]);
+        *reinterpret_cast<float2*>(p0 + 8 * ATT_D) = make_float2(o[n][2], o[n][3]);
     }
-    if (t4 == 0) {
-        mML[(warp * 16 + g) * 2] = m_run[0]; mML[(warp * 16 + g) * 2 + 1] = l_run[0];
-        mML[(warp * 16 + g + 8) * 2] = m_run[1]; mML[(warp * 16 + g + 8) * 2 + 1] = l_run[1];
+    if (t4 == 0 && dh == 0) {
+        mML[(kg * 16 + g) * 2] = m_run[0]; mML[(kg * 16 + g) * 2 + 1] = l_run[0];
+        mML[(kg * 16 + g + 8) * 2] = m_run[1]; mML[(kg * 16 + g + 8) * 2 + 1] = l_run[1];
     }
     __syncthreads();
-    float* part = a.part + (((size_t)b * ATT_KV + kvh) * a.max_splits + split) * PART_STRIDE;
+    const int* pbase = meta_base(a.meta, P);
+    const int nsp = pbase[pair + 1] - pbase[pair];                   // blocks that share this pair
+    float* part = a.part + (size_t)slot * PART_STRIDE;
+    __nv_bfloat16* out_pair = a.out + ((size_t)b * M * ATT_H + kvh * ATT_GQA) * ATT_D;     // row r = j*4 + hq -> out[(b*M + j), kvh*4 + hq]
     for (int r = 0; r < 4 * M; r++) {
-        float mw[ATT_WARPS], mstar = -INFINITY;
+        float mw[KGROUPS], mstar = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; w++) { mw[w] = mML[(w * 16 + r) * 2]; mstar = fmaxf(mstar, mw[w]); }
-        float wgt[ATT_WARPS], lsum = 0.f;
+        for (int w = 0; w < KGROUPS; w++) { mw[w] = mML[(w * 16 + r) * 2]; mstar = fmaxf(mstar, mw[w]); }
+        float wgt[KGROUPS], lsum = 0.f;
 #pragma unroll
-        for (int w = 0; w < ATT_WARPS; w++) { wgt[w] = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - mstar); lsum += wgt[w] * mML[(w * 16 + r) * 2 + 1]; }
-        {
-            const int d = tid;                                           // 256 threads = 256 dims
-            float acc = 0.f;
+        for (int w = 0; w < KGROUPS; w++) { wgt[w] = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - mstar); lsum += wgt[w] * mML[(w * 16 + r) * 2 + 1]; }
+        const int d = tid;                                               // 256 threads = 256 dims
+        float acc = 0.f;
 #pragma unroll
-            for (int w = 0; w < ATT_WARPS; w++) acc += wgt[w] * mO[(w * 16 + r) * ATT_D + d];
+        for (int w = 0; w < KGROUPS; w++) acc += wgt[w] * mO[(w * 16 + r) * ATT_D + d];
+        if (nsp == 1) {                                                  // the whole pair was this block's: no partial, no merge
+            const float inv = lsum == 0.f ? 1.f : 1.f / lsum;          // sum == 0 guard as qwen35/batch.py:216
+            out_pair[((size_t)(r >> 2) * ATT_H + (r & 3)) * ATT_D + d] = __float2bfloat16_rn(acc * inv);
+        } else {
             part[r * ATT_D + d] = acc;
+            if (tid == 0) { part[16 * ATT_D + 2 * r] = mstar; part[16 * ATT_D + 2 * r + 1] = lsum; }
         }
-        if (tid == 0) { part[16 * ATT_D + 2 * r] = mstar; part[16 * ATT_D + 2 * r + 1] = lsum; }
     }
-}
-
-// merge the splits of one (row, query head): 128 threads x 2 dims
-__global__ void __launch_bounds__(128) gqa_decode_merge_kernel(const AttnArgs a) {
-    const int r = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-    const int b = r / a.M, j = r % a.M, kvh = h / ATT_GQA, row = j * 4 + (h % ATT_GQA);
-    const int ctx = a.ctx_len[b];
-    if (ctx < 0 || (long long)ctx + a.M > (long long)a.max_pages * a.page_size) return;
-    const int nsp = n_splits_of(ctx, a.split_keys);
-    const float* base = a.part + ((size_t)b * ATT_KV + kvh) * a.max_splits * PART_STRIDE;
-    float mstar = -INFINITY;
-    for (int s = 0; s < nsp; s++) mstar = fmaxf(mstar, base[(size_t)s * PART_STRIDE + 16 * ATT_D + 2 * row]);
-    float acc0 = 0.f, acc1 = 0.f, lsum = 0.f;
-    for (int s = 0; s < nsp; s++) {
-        const float* p = base + (size_t)s * PART_STRIDE;
-        const float m = p[16 * ATT_D + 2 * row];
-        const float w = (m == -INFINITY) ? 0.f : exp2f(m - mstar);
-        lsum += w * p[16 * ATT_D + 2 * row + 1];
-        acc0 += w * p[row * ATT_D + tid];
-        acc1 += w * p[row * ATT_D + tid + 128];
+    if (nsp > 1) {
+        // the block that writes the last partial of a pair merges them (the counters were zeroed by this call's plan kernel)
+        __shared__ int s_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) s_last = atomicAdd(meta_count(a.meta, P) + pair, 1) == nsp - 1;
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            const float* pb = a.part + (size_t)pbase[pair] * PART_STRIDE;
+            // weights of every (row, partial) first (the staging memory is free here), then 16 independent accumulators per thread
+            float* wsm = mO;                                             // [nsp][16] weights, then [16] 1 / sum
+            for (int i = tid; i < nsp * 16; i += ATT_THREADS) wsm[i] = __ldcg(pb + (size_t)(i >> 4) * PART_STRIDE + 16 * ATT_D + 2 * (i & 15));
+            __syncthreads();
+            if (tid < 16) {
+                float ms = -INFINITY, lsum = 0.f;
+                for (int sp = 0; sp < nsp; sp++) ms = fmaxf(ms, wsm[sp * 16 + tid]);
+                for (int sp = 0; sp < nsp; sp++) {
+                    const float m = wsm[sp * 16 + tid];
+                    const float w = (m == -INFINITY) ? 0.f : exp2f(m - ms);
+                    lsum += w * __ldcg(pb + (size_t)sp * PART_STRIDE + 16 * ATT_D + 2 * tid + 1);
+                    wsm[sp * 16 + tid] = w;
+                }
+                wsm[nsp * 16 + tid] = lsum == 0.f ? 1.f : 1.f / lsum;   // sum == 0 guard as qwen35/batch.py:216
+            }
+            __syncthreads();
+            float acc[16];
+#pragma unroll
+            for (int r = 0; r < 16; r++) acc[r] = 0.f;
+            for (int sp = 0; sp < nsp; sp++) {
+                const float* pp = pb + (size_t)sp * PART_STRIDE + tid;
+#pragma unroll
+                for (int r = 0; r < 16; r++)
+                    if (r < 4 * M) acc[r] += wsm[sp * 16 + r] * __ldcg(pp + r * ATT_D);
+            }
+#pragma unroll
+            for (int r = 0; r < 16; r++)
+                if (r < 4 * M) out_pair[((size_t)(r >> 2) * ATT_H + (r & 3)) * ATT_D + tid] = __float2bfloat16_rn(acc[r] * wsm[nsp * 16 + r]);
+        }
     }
-    const float inv = lsum == 0.f ? 1.f : 1.f / lsum;                  // sum == 0 guard as qwen35/batch.py:216
-    __nv_bfloat16* o = a.out + ((size_t)r * ATT_H + h) * ATT_D;
-    o[tid] = __float2bfloat16_rn(acc0 * inv);
-    o[tid + 128] = __float2bfloat16_rn(acc1 * inv);
+    __syncthreads();                                                 // shared memory is reused by the block's next pair
+  }
 }
 
-// split size (keys): a block has a fixed cost (pipeline fill, the merge of its eight warps, its partial) of several tile times, so
-// splits are as long as they can be while a batch of B sequences of up to max_ctx keys still gives about one block per SM
-void gqa_split_plan(int B, int max_ctx, int* split_keys, int* max_splits) {
-    long long sk = (long long)max_ctx * B * ATT_KV / 200;
-    sk = (sk / TK) * TK;
-    if (sk < 2 * TK) sk = 2 * TK;
-    if (sk > 4096) sk = 4096;
-    int ms = (int)((max_ctx + sk - 1) / sk);
-    if (ms < 1) ms = 1;
-    *split_keys = (int)sk;
-    *max_splits = ms;
+// ---- host side ----
+static int sm_count() {
+    static int sms[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return 148; }
+    if (!sms[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) { cudaGetLastError(); n = 148; }
+        sms[dev] = n;
+    }
+    return sms[dev];
 }
 
+// workspace = plan (ints) + one partial per (block, pair) intersection: at most blocks + pairs of them
 size_t gqa_workspace_bytes(int B, int max_ctx) {
-    int sk, ms;
-    gqa_split_plan(B, max_ctx, &sk, &ms);
-    return (size_t)B * ATT_KV * ms * PART_STRIDE * sizeof(float);
+    (void)max_ctx;
+    const int P = B * ATT_KV;
+    return meta_ints(P) * sizeof(int) + (size_t)(sm_count() + P) * PART_STRIDE * sizeof(float);
 }
 
-int launch_gqa_decode(AttnArgs a, int max_ctx, cudaStream_t stream) {
-    if (a.B <= 0) return GDN_OK;
-    gqa_split_plan(a.B, max_ctx, &a.split_keys, &a.max_splits);
+static int launch_with_workspace(AttnArgs a, void* ws, size_t ws_bytes, const char* who, cudaStream_t stream) {
+    a.P = a.B * ATT_KV;
+    const size_t meta_b = meta_ints(a.P) * sizeof(int);
+    const long long slots = ws_bytes > meta_b ? (long long)((ws_bytes - meta_b) / (PART_STRIDE * sizeof(float))) : 0;
+    a.G = sm_count();
+    if (slots - a.P < a.G) a.G = (int)(slots - a.P);                 // a smaller workspace is served with fewer blocks
+    if (a.G < 1) {
+        set_error("%s: scratch of %zu bytes cannot hold the plan and %d + 1 partials of %zu bytes", who, ws_bytes, a.P,
+                  (size_t)PART_STRIDE * sizeof(float));
+        return GDN_E_SHAPE;
+    }
+    a.meta = static_cast<int*>(ws);
+    a.part = reinterpret_cast<float*>(static_cast<char*>(ws) + meta_b);
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 64 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         if (cudaFuncSetAttribute(gqa_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess)
             return check_launch("gqa_decode smem attribute");
         attr_set[dev] = true;
     }
-    gqa_decode_split_kernel<<<dim3(a.max_splits, ATT_KV, a.B), ATT_THREADS, ATT_SMEM, stream>>>(a);
-    int rc = check_launch("gqa_decode_split");
+    gqa_decode_plan_kernel<<<1, 256, 0, stream>>>(a);
+    int rc = check_launch("gqa_decode_plan");
     if (rc) return rc;
-    gqa_decode_merge_kernel<<<dim3(a.B * a.M, ATT_H), 128, 0, stream>>>(a);
-    return check_launch("gqa_decode_merge");
+    gqa_decode_split_kernel<<<a.G, ATT_THREADS, ATT_SMEM, stream>>>(a);
+    return check_launch("gqa_decode_split");
+}
+
+int launch_gqa_decode(AttnArgs a, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+    if (a.B <= 0) return GDN_OK;
+    return launch_with_workspace(a, workspace, workspace_bytes, "gqa_decode_paged", stream);
 }
 
 // ----------------------------------------------------------------------------------------------------------------------
-// Variant for callers that cannot allocate device memory: the split-KV partials go to a fixed array that lives in the library
-// image instead of a caller-provided workspace.  Every GPU that loads the library holds these 12 MiB until the process exits.
-// The array is shared by all calls on a device and keeps whatever the last call left in it; nothing in it has to start at zero
-// (every partial that the merge kernel reads was written by the split kernel of the same call), but two calls that overlap on
-// the GPU (different streams) would overwrite each other's partials.
+// Variant for callers that cannot allocate device memory: the plan and the partials go to a fixed array that lives in the
+// library image instead of a caller-provided workspace.  Every GPU that loads the library holds these 12 MiB until the process
+// exits.  The array is shared by all calls on a device and keeps whatever the last call left in it; nothing in it has to start
+// at zero (the plan kernel of a call rewrites the plan, and every partial that the merge kernel reads was written by the split
+// kernel of the same call), but two calls that overlap on the GPU (different streams) would overwrite each other's data.
 // ----------------------------------------------------------------------------------------------------------------------
-constexpr int STATIC_PARTIALS = 762;                                   // (sequence, kv head, split) triples that fit
-static __device__ __align__(256) float g_static_partials[(size_t)STATIC_PARTIALS * PART_STRIDE];      // 12 MiB
+constexpr int STATIC_PARTIALS = 762;                                   // partial slots that fit next to the plan
+constexpr int STATIC_MAX_B = 256;                                      // sequences per call: 2 * 256 pairs + one block per SM <= 762
+static __device__ __align__(256) float g_static_scratch[(size_t)STATIC_PARTIALS * PART_STRIDE + 2048];      // 12 MiB
 
-int gqa_static_max_partials() { return STATIC_PARTIALS; }
-
-int launch_gqa_decode_static(AttnArgs a, int max_ctx, cudaStream_t stream) {
+int launch_gqa_decode_static(AttnArgs a, cudaStream_t stream) {
     if (a.B <= 0) return GDN_OK;
-    int sk, ms;
-    gqa_split_plan(a.B, max_ctx, &sk, &ms);
-    const long long need = (long long)a.B * ATT_KV * ms;
-    if (need > STATIC_PARTIALS) {
-        set_error("gqa_decode_paged_static: B=%d sequences of up to %d tokens need %lld split partials, the built-in scratch holds %d "
-                  "(use gqa_decode_paged with a workspace of gqa_decode_workspace_bytes() instead)", a.B, max_ctx, need, STATIC_PARTIALS);
+    if (a.B > STATIC_MAX_B) {
+        set_error("gqa_decode_paged_static: B=%d sequences exceed the %d the built-in scratch is sized for (%d partial slots; "
+                  "use gqa_decode_paged with a workspace of gqa_decode_workspace_bytes() instead)", a.B, STATIC_MAX_B, STATIC_PARTIALS);
         return GDN_E_SHAPE;
     }
     // In host code the array's name is only a handle: the device address has to be asked for, once per device, with that device
@@ -356,7 +490,7 @@ int launch_gqa_decode_static(AttnArgs a, int max_ctx, cudaStream_t stream) {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return check_launch("gqa_decode_paged_static: device");
     if (!addr[dev]) {
         float* p = nullptr;
-        const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_partials);
+        const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_scratch);
         if (e != cudaSuccess || !p) {
             cudaGetLastError();
             set_error("gqa_decode_paged_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
@@ -364,8 +498,7 @@ int launch_gqa_decode_static(AttnArgs a, int max_ctx, cudaStream_t stream) {
         }
         addr[dev] = p;
     }
-    a.part = addr[dev];
-    return launch_gqa_decode(a, max_ctx, stream);
+    return launch_with_workspace(a, addr[dev], sizeof(float) * ((size_t)STATIC_PARTIALS * PART_STRIDE + 2048), "gqa_decode_paged_static", stream);
 }
 
 }  // namespace gdn

@@ -48,15 +48,16 @@ struct AttnArgs {
     const int* block_table;                     // [B, max_pages]
     const int* ctx_len;                         // [B] tokens already cached
     __nv_bfloat16* out;                         // [B*M,8,256]
-    float* part;                                // workspace [B, 2, max_splits, PART_STRIDE]
+    int* meta;                                  // work plan in the workspace (tile and partial-slot prefix sums per pair)
+    float* part;                                // fp32 partials in the workspace: [slots][PART_STRIDE]
     int* status;
-    int B, M, page_size, max_pages, n_pages, split_keys, max_splits;
+    int B, M, page_size, max_pages, n_pages;
+    int P, G;                                   // pairs (= 2 B) and persistent blocks; filled in by the launcher
 };
 
 size_t gqa_workspace_bytes(int B, int max_ctx);
-int launch_gqa_decode(AttnArgs a, int max_ctx, cudaStream_t stream);
-int launch_gqa_decode_static(AttnArgs a, int max_ctx, cudaStream_t stream);
-int gqa_static_max_partials();
+int launch_gqa_decode(AttnArgs a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+int launch_gqa_decode_static(AttnArgs a, cudaStream_t stream);
 
 // ---- gdn_prefill_sm100.cu ----
 struct PrefillArgs {

@@ -63,7 +63,7 @@ def test_static_scratch_entry_matches_workspace_entry(dev):
 def test_static_scratch_rejects_oversized_batches(dev):
     lib = _lib.load()
     one = ctypes.c_void_p(256)
-    rc = lib.gqa_decode_paged_static(one, one, one, one, one, one, one, one, 64, 1, 64, 2048, 4096, 131072, None)
+    rc = lib.gqa_decode_paged_static(one, one, one, one, one, one, one, one, 300, 1, 64, 2048, 4096, 131072, None)
     assert rc == -1
     msg = lib.gdn_last_error_string().decode()
-    assert "762" in msg and "gqa_decode_paged" in msg
+    assert "256" in msg and "gqa_decode_paged" in msg
