@@ -32,8 +32,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
 // Bounded wait: gives up after `limit` polls and returns false.  The caller records the failure and leaves the kernel
 // instead of spinning for ever on a shared GPU.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = 200000u) {
-    for (uint32_t i = 0; i < limit; i++)
+    for (uint32_t i = 0; i < limit; i++) {
         if (mbar_try_wait(bar, parity)) return true;
+#ifdef GDN_POLL_SLEEP
+        __nanosleep(GDN_POLL_SLEEP);
+#endif
+    }
     return false;
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
