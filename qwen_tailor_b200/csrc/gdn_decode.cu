@@ -309,6 +309,10 @@ static int launch_mt(const DecodeArgs& a, cudaStream_t stream) {
     const int n_sm = (dev >= 0 && dev < 64 && sms[dev] > 0) ? sms[dev] : 148;
     const int n_slices = a.B * HV * SLICES_PER_HEAD;
     int grid = Tune<MT>::BLOCKS * n_sm;
+    const int n_heads = a.B * HV;
+    // small batches: one block per head (4 slices, one prologue, a full ring) beats more blocks with 1-2 slices and a prologue
+    // each; very small ones (fewer heads than SMs) fall back to one slice per block so that every SM has work
+    if (n_heads <= grid && n_heads >= n_sm) grid = n_heads;
     if (grid > n_slices) grid = n_slices;
     gdn_decode_kernel<MT><<<grid, 128, smem, stream>>>(a, n_slices);
     return check_launch("gdn_decode");
