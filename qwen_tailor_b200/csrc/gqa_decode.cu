@@ -10,8 +10,9 @@
 //   * balanced split-KV: the 64-key tiles of all (sequence, kv head) pairs form one list (a tiny plan kernel builds its prefix
 //     sums from ctx_len on the device), and one persistent block per SM takes a contiguous 1/n-th of it, so a ragged batch
 //     loads every SM equally whatever the context lengths are.  Where a block's range crosses from one pair to the next, or
-//     ends inside one, it writes a partial (max, sum, O) to a caller-provided fp32 workspace; a merge kernel combines the
-//     1..few partials of each pair.
+//     ends inside one, it writes a partial (max, sum, O) to a caller-provided fp32 workspace; the block that writes the
+//     last partial of a pair (an arrival counter tells it) merges them and stores the bf16 rows.  A pair that lies inside one
+//     block's range is stored directly.
 //   * GQA packing: the 4 query heads of a KV head times the M <= 4 chained rows form the 16 rows of a warp-level
 //     m16n8k16 bf16 MMA, so each K/V byte is read once for up to 16 query rows (at M = 4 plain FMAs could not keep up with
 //     HBM).  The 8 warps are 4 key groups x 2 halves of the head dim: a warp computes the scores of its 16 keys of a tile
@@ -469,7 +470,7 @@ int launch_gqa_decode(AttnArgs a, void* workspace, size_t workspace_bytes, cudaS
 // Variant for callers that cannot allocate device memory: the plan and the partials go to a fixed array that lives in the
 // library image instead of a caller-provided workspace.  Every GPU that loads the library holds these 12 MiB until the process
 // exits.  The array is shared by all calls on a device and keeps whatever the last call left in it; nothing in it has to start
-// at zero (the plan kernel of a call rewrites the plan, and every partial that the merge kernel reads was written by the split
+// at zero (the plan kernel of a call rewrites the plan, and every partial that a merging block reads was written by the split
 // kernel of the same call), but two calls that overlap on the GPU (different streams) would overwrite each other's data.
 // ----------------------------------------------------------------------------------------------------------------------
 constexpr int STATIC_PARTIALS = 762;                                   // partial slots that fit next to the plan
