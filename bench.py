@@ -310,6 +310,68 @@ def bench_prefill(torch, dev, args, peaks, T=2048, n_layers=N_LAYERS):
                 hbm=dict(achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"]))
 
 
+def bench_prefill_ragged(torch, dev, args, peaks, n_layers=6):
+    """Configuration 4: 16 sequences ~U[128, 4096] packed by cu_seqlens, every second one resuming from a cached fp32 state at a
+    64-aligned prefix (only the suffix is computed); here n_layers independent layers per launch."""
+    import numpy as np
+    from qwen_tailor_b200 import synth
+    from qwen_tailor_b200.gdn_nax import gdn_chunked_varlen
+    lengths, prefix = synth.config4_lengths()
+    suffix = (lengths - prefix).astype(np.int64)
+    n_seq = len(suffix)
+    cu = np.zeros(n_layers * n_seq + 1, np.int64)
+    cu[1:] = np.cumsum(np.tile(suffix, n_layers))
+    total = int(cu[-1])
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+    rn = lambda *s: torch.randn(s, generator=g, device=dev, dtype=torch.float32)
+    unit = lambda x: x / x.norm(dim=-1, keepdim=True)
+    q = (unit(rn(total, HV, DK)) * DK ** -0.5).to(torch.bfloat16)
+    k = unit(rn(total, HV, DK)).to(torch.bfloat16)
+    v = rn(total, HV, DV).to(torch.bfloat16)
+    lg = -torch.exp(torch.rand((1, HV), generator=g, device=dev) * math.log(16.0)) * torch.nn.functional.softplus(rn(total, HV))
+    beta = torch.sigmoid(rn(total, HV))
+    init = rn(n_seq, HV, DV, DK) * 0.02
+    idx = torch.tensor(np.tile(np.where(prefix > 0, np.arange(n_seq), -1), n_layers), dtype=torch.int32, device=dev)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=dev)
+
+    def step():
+        gdn_chunked_varlen(q, k, v, lg.contiguous(), beta, cu_t, init_state=init, init_idx=idx)
+
+    for _ in range(3):
+        step()
+    ms = time_region(torch, step, args.steps) / args.steps
+    tflops = total * PREFILL_FLOP_PER_TOKEN_LAYER / (ms * 1e-3) / 1e12
+    return dict(workload=f"GDN ragged prefill, config 4: 16 sequences ~U[128,4096] with prefix resume, {n_layers} layers per launch", ms_per_step=ms,
+                tokens_per_s=total / (ms * 1e-3), roofline=dict(bound="tensor", achieved=tflops, peak=peaks["bf16_tflops"], unit="TFLOP/s",
+                                                                frac=tflops / peaks["bf16_tflops"]))
+
+
+def bench_prefill_head_sharded(torch, dev, args, dist, peaks, T=8192):
+    """Configuration 3, head-parallel: one sequence of T tokens, the 16 heads split over the ranks, y all-gathered over NCCL."""
+    from qwen_tailor_b200.shard import prefill_head_sharded
+    world, rank = dist.get_world_size(), dist.get_rank()
+    g = torch.Generator(device=dev)
+    g.manual_seed(100)
+    rn = lambda *s: torch.randn(s, generator=g, device=dev, dtype=torch.float32)
+    unit = lambda x: x / x.norm(dim=-1, keepdim=True)
+    q = (unit(rn(T, HV, DK)) * DK ** -0.5).to(torch.bfloat16)
+    k = unit(rn(T, HV, DK)).to(torch.bfloat16)
+    v = rn(T, HV, DV).to(torch.bfloat16)
+    lg = (-torch.exp(torch.rand((1, HV), generator=g, device=dev) * math.log(16.0)) * torch.nn.functional.softplus(rn(T, HV))).contiguous()
+    beta = torch.sigmoid(rn(T, HV))
+    cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+
+    def step():
+        prefill_head_sharded(q, k, v, lg, beta, cu, rank, world)
+
+    for _ in range(3):
+        step()
+    ms = time_region(torch, step, args.steps, dist) / args.steps
+    return dict(workload=f"GDN prefill, config 3 head-parallel: B=1, T={T}, 16 heads over {world} GPUs, NCCL all-gather of y", ms_per_step=ms,
+                tokens_per_s=T / (ms * 1e-3))
+
+
 # ----------------------------------------------------------------------------------------------------------------------
 # CPU baseline (OpenMP C port of the reference's arithmetic; test infrastructure, timed only)
 # ----------------------------------------------------------------------------------------------------------------------
@@ -437,12 +499,21 @@ def main():
             p = bench_prefill(torch, dev, a2, peaks)
             if p is not None:
                 extra["prefill_T2048"] = p
+                extra["prefill_T8192"] = bench_prefill(torch, dev, a2, peaks, T=8192, n_layers=9)
+                extra["prefill_ragged_config4"] = bench_prefill_ragged(torch, dev, a2, peaks)
         line["extra"] = extra
         if not args.no_cpu:
             v, ms, cores = cpu_decode_steps(3, 1)
             line["cpu_baseline"] = dict(value=v, unit="steps/s", cores=cores, kind="port",
                                         sample="3 full steps (64 sequences x 18 layers each) after 1 warm-up, OpenMP C port of the reference's decode arithmetic")
         assert _lib.device_status() == 0, "a kernel reported an out-of-range index"
+    if world > 1 and not args.no_extra:
+        import copy
+        a3 = copy.copy(args)
+        a3.steps = max(5, args.steps // 4)
+        hs = bench_prefill_head_sharded(torch, dev, a3, dist, peaks)
+        if rank == 0:
+            line["extra"] = {"prefill_T8192_head_sharded": hs}
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:
