@@ -377,6 +377,8 @@ def bench_prefill_head_sharded(torch, dev, args, dist, peaks, T=8192):
 # ----------------------------------------------------------------------------------------------------------------------
 def cpu_decode_steps(n_steps, warmup, B=B_DECODE, n_layers=N_LAYERS):
     import numpy as np
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU baseline is meant to use every host core
+    os.environ["OMP_NUM_THREADS"] = os.environ.get("GDN_CPU_THREADS", str(os.cpu_count() or 1))
     from oracle import build_oracle as co
     rng = np.random.default_rng(1)
     conv_w = (rng.integers(0, 1 << 15, CD * 4)).astype(np.uint16)
