@@ -240,10 +240,10 @@ def bench_attention(torch, dev, args, peaks, n_layers=6):
                 kv_gb=byts / 1e9, roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"]))
 
 
-def bench_verify(torch, dev, args, peaks, n_layers=N_LAYERS):
-    """Configuration 5, GDN part: B=16 sequences x M=4 chained tokens through 18 layers, per-token fp32 snapshots in place."""
+def bench_verify(torch, dev, args, peaks, n_layers=N_LAYERS, B=16):
+    """Configuration 5, GDN part: B sequences x M=4 chained tokens through n_layers layers, per-token fp32 snapshots in place."""
     from qwen_tailor_b200.batch_spec import deltanet_bm
-    B, M = 16, 4
+    M = 4
     g = torch.Generator(device=dev)
     g.manual_seed(11)
     layers = []
@@ -266,7 +266,7 @@ def bench_verify(torch, dev, args, peaks, n_layers=N_LAYERS):
     ms = time_region(torch, graphed(torch, step), args.steps) / args.steps
     per = (1 + M) * STATE_BYTES + M * (CD * 2 + 3 * CD * 2 + HV * DV * 2) + 3 * CD * 2
     gbs = n_layers * B * per / (ms * 1e-3) / 1e9
-    return dict(workload="GDN speculative verify, config 5: B=16, M=4, 18 layers, snapshots [B,4,16,128,128] fp32 in place", ms_per_step=ms,
+    return dict(workload=f"GDN speculative verify, config 5 shape: B={B}, M=4, {n_layers} layers, snapshots [B,4,16,128,128] fp32 in place", ms_per_step=ms,
                 roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"]))
 
 
@@ -468,7 +468,7 @@ def main():
         elif args.case == "attention":
             out = bench_attention(torch, dev, a2, peaks, n_layers=2)
         else:
-            out = bench_verify(torch, dev, a2, peaks, n_layers=4)
+            out = [bench_verify(torch, dev, a2, peaks, n_layers=4), bench_verify(torch, dev, a2, peaks, n_layers=4, B=64)]
         print(json.dumps(out))
         return
 
@@ -497,6 +497,7 @@ def main():
                 d = bench_decode(torch, dev, a2, None, peaks, B=B, with_e2e=False)
                 extra[f"decode_B{B}"] = dict(steps_per_s=1e3 / d["ms_per_step"], launch_us=d["launch_us"], hbm_gbs=d["achieved_gbs"], frac=d["frac"])
             extra["verify_config5"] = bench_verify(torch, dev, a2, peaks)
+            extra["verify_B64_M4"] = bench_verify(torch, dev, a2, peaks, n_layers=6, B=64)
             extra["attention_config5"] = bench_attention(torch, dev, a2, peaks)
             p = bench_prefill(torch, dev, a2, peaks)
             if p is not None:
