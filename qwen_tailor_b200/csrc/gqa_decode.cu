@@ -23,8 +23,11 @@
 //     (one thread per key) and shared through shared memory.
 //   * the probabilities are fed to the P.V MMA as a bf16 hi + lo pair, so the result carries fp32-level accuracy like the
 //     reference's fp32 accumulation of exp_score * v.
+#include <cuda.h>
+#include <cstring>
 #include "gdn_common.cuh"
 #include "launchers.cuh"
+#include "sm100_prims.cuh"
 
 namespace gdn {
 
@@ -61,6 +64,9 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
 }
 // byte offset of 16-byte chunk `c` of row `r` in a swizzled [rows][512 B] tile
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)(r * ROWB + ((c ^ (r & 7)) << 4)); }
+
+// byte offset of 16-byte chunk `c` of key row `r` in a tile that TMA wrote as four [64 keys][64 dims] boxes with the 128-byte swizzle
+__device__ __forceinline__ uint32_t swz_t(int r, int c) { return (uint32_t)((c >> 3) * 8192 + r * 128 + (((c & 7) ^ (r & 7)) << 4)); }
 
 // ---- work plan in the workspace: ints meta[0] = total tiles, meta[1] = working blocks, then cum[P+1] (tile prefix sums per (sequence, kv head) pair),
 //      base[P+1] (partial-slot prefix sums), first[P] (first block of each pair), count[P] (arrival counters, zeroed by the plan
@@ -126,8 +132,15 @@ __global__ void __launch_bounds__(256) gqa_decode_plan_kernel(const AttnArgs a) 
     for (int p = tid; p < P; p += 256) count[p] = 0;
 }
 
-__global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const AttnArgs a) {
+// TMA = false: every warp gathers its share of a tile with 16-byte cp.async (any page size).
+// TMA = true (pages hold a multiple of 64 keys, so a tile lies inside one page): a ninth warp is the producer -- one lane issues
+// eight tensor-map copies per tile into a three-stage ring guarded by full / empty mbarriers, the eight math warps never issue
+// or wait for copies and meet no block-wide barrier inside a pair.
+template <bool TMA>
+__global__ void __launch_bounds__(TMA ? ATT_THREADS + 32 : ATT_THREADS, 1)
+gqa_decode_split_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
     extern __shared__ __align__(1024) unsigned char smem[];
+    __shared__ uint64_t ring_bar[2 * ATT_STAGES + 1];               // full[3], empty[3], pair finished (TMA path)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
     const int M = a.M, P = a.P;
     const int* cum = meta_cum(a.meta);
@@ -137,6 +150,21 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
     long long lo = (long long)blockIdx.x * N / G;
     const long long hi = (long long)(blockIdx.x + 1) * N / G;
     if (lo >= hi) return;
+    const bool producer = TMA && warp == 8;
+    auto csync = [&]() {                                             // barrier among the 256 math threads
+        if (TMA) asm volatile("bar.sync 1, 256;" ::: "memory"); else __syncthreads();
+    };
+    auto rbar = [&](int i) -> uint32_t { return smem_u32(&ring_bar[i]); };
+    uint32_t ring_n = 0;                                             // tiles this block has put through the ring so far (TMA path)
+    uint32_t pairs_done = 0;
+    if (TMA) {
+        if (tid == 0) {
+            for (int i = 0; i < ATT_STAGES; i++) { sm100::mbar_init(rbar(i), 1); sm100::mbar_init(rbar(ATT_STAGES + i), 8); }
+            sm100::mbar_init(rbar(2 * ATT_STAGES), 8);
+            sm100::fence_barrier_init();
+        }
+        __syncthreads();
+    }
     int pair;                                                        // pair that owns tile lo: cum[pair] <= lo < cum[pair + 1]
     {
         int l = 0, r = P - 1;
@@ -162,6 +190,49 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
     const uint32_t sKV = sQ + 16 * ROWB;
     const int* table = a.block_table + (size_t)b * a.max_pages;
 
+    if (producer) {
+        // ---- producer warp: keep the ring full with the tiles [ta, tb) of this pair ----
+        // the math warps use the staging memory as scratch when they merge at the end of a pair: wait until the previous pair is done
+        if (pairs_done > 0 && !sm100::mbar_wait(rbar(2 * ATT_STAGES), (pairs_done - 1) & 1u)) { if (lane == 0) atomicExch(a.status, 2); return; }
+        pairs_done++;
+        for (int t = 0; t < ntiles; t++, ring_n++) {
+            const int stage = ring_n % ATT_STAGES;
+            if (ring_n >= ATT_STAGES && !sm100::mbar_wait(rbar(ATT_STAGES + stage), ((ring_n / ATT_STAGES) - 1) & 1u)) { if (lane == 0) atomicExch(a.status, 2); return; }
+            const uint32_t dK = sKV + stage * 2 * TILE_BYTES, dV = dK + TILE_BYTES;
+            if (t < ctx_tiles) {
+                if (lane == 0) {
+                    const int key = k_begin + t * TK;
+                    int page = table[key / a.page_size];
+                    if (page < 0 || page >= a.n_pages) { atomicExch(a.status, 1); page = 0; }
+                    const int row = key % a.page_size;
+                    sm100::mbar_expect_tx(rbar(stage), 2 * TILE_BYTES);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                                     ::"r"(dK + j * 8192), "l"(&tmK), "r"(rbar(stage)), "r"(64 * j), "r"(row), "r"(kvh), "r"(page) : "memory");
+                        asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                                     ::"r"(dV + j * 8192), "l"(&tmV), "r"(rbar(stage)), "r"(64 * j), "r"(row), "r"(kvh), "r"(page) : "memory");
+                    }
+                }
+            } else {
+                // the rows of this call: copied from k_new / v_new by the 32 lanes; V rows M..15 are zeroed (key group 0 reads 16 rows)
+                for (int i = lane; i < 16 * 32; i += 32) {
+                    const int r = i >> 5, c = i & 31;
+                    uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
+                    if (r < M) {
+                        const size_t off = (((size_t)b * M + r) * ATT_KV + kvh) * ATT_D;
+                        kv4 = reinterpret_cast<const uint4*>(a.k_new + off)[c];
+                        vv4 = reinterpret_cast<const uint4*>(a.v_new + off)[c];
+                    }
+                    *reinterpret_cast<uint4*>(smem + 16 * ROWB + stage * 2 * TILE_BYTES + swz_t(r, c)) = kv4;
+                    *reinterpret_cast<uint4*>(smem + 16 * ROWB + stage * 2 * TILE_BYTES + TILE_BYTES + swz_t(r, c)) = vv4;
+                }
+                __syncwarp();
+                if (lane == 0) sm100::mbar_arrive(rbar(stage));
+            }
+        }
+        continue;
+    }
     // ---- append the new rows to the cache (first split only; readers take them from the inputs) ----
     if (split == 0) {
         for (int i = tid; i < M * 64; i += ATT_THREADS) {
@@ -225,29 +296,42 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
     const float sc = 0.0625f * 1.4426950408889634f;          // 256^-1/2 (qwen35/batch.py:176), scores kept in log2 units
 
     // prologue: plan the first three tiles, start the first two
-    for (int t = 0; t < ATT_STAGES && t < ntiles; t++) plan_tile(t, t);
-    __syncthreads();
-    for (int t = 0; t < ATT_STAGES - 1; t++) {
-        if (t < ntiles) load_tile(t);
-        cp_async_commit();
-    }
-    for (int t = 0; t < ntiles; t++) {
-        const int stage = t % ATT_STAGES;
-        // tile t+2 goes into the stage that tile t-1 used (all warps left it at the barrier that ended iteration t-1)
-        if (t + ATT_STAGES - 1 < ntiles) load_tile((t + ATT_STAGES - 1) % ATT_STAGES);
-        cp_async_commit();
-        cp_async_wait<ATT_STAGES - 1>();
+    if (!TMA) {
+        for (int t = 0; t < ATT_STAGES && t < ntiles; t++) plan_tile(t, t);
         __syncthreads();
+        for (int t = 0; t < ATT_STAGES - 1; t++) {
+            if (t < ntiles) load_tile(t);
+            cp_async_commit();
+        }
+    } else {
+        csync();                                                     // Q rows are in place
+    }
+    bool ring_ok = true;
+    for (int t = 0; t < ntiles; t++) {
+        const int stage = TMA ? (int)(ring_n % ATT_STAGES) : t % ATT_STAGES;
+        if (!TMA) {
+            // tile t+2 goes into the stage that tile t-1 used (all warps left it at the barrier that ended iteration t-1)
+            if (t + ATT_STAGES - 1 < ntiles) load_tile((t + ATT_STAGES - 1) % ATT_STAGES);
+            cp_async_commit();
+            cp_async_wait<ATT_STAGES - 1>();
+            __syncthreads();
+        } else {
+            ring_ok = ring_ok && sm100::mbar_wait(rbar(stage), (ring_n / ATT_STAGES) & 1u);
+        }
 
         const bool new_tile = t >= ctx_tiles;
         const int key0 = new_tile ? 0 : k_begin + t * TK;               // position of the tile's first key in its own numbering
         const int limit = new_tile ? M : k_end - key0;                   // keys of the tile that exist
-#ifdef ATT_EXPERIMENT_NO_COMPUTE
-        if (kg * KPW < limit && t < 0) {
-#else
         if (kg * KPW < limit) {
-#endif
             const uint32_t tK = sKV + stage * 2 * TILE_BYTES, tV = tK + TILE_BYTES;
+            auto kvoff = [&](int r, int c) -> uint32_t { return TMA ? swz_t(r, c) : swz(r, c); };
+            if (TMA && !new_tile && limit < kg * KPW + KPW) {
+                // the tensor-map copy brought whole 64-key boxes: value rows past the end of the context hold whatever the page
+                // holds there and must not reach the MMA (0 x NaN); both warps of the key group write the same zeros
+                for (int i = lane; i < (kg * KPW + KPW - limit) * 32; i += 32)
+                    *reinterpret_cast<uint4*>(smem + 16 * ROWB + stage * 2 * TILE_BYTES + TILE_BYTES + swz_t(limit + (i >> 5), i & 31)) = make_uint4(0, 0, 0, 0);
+                __syncwarp();
+            }
             float sc2[2][4];
 #pragma unroll
             for (int n = 0; n < 2; n++) { sc2[n][0] = sc2[n][1] = sc2[n][2] = sc2[n][3] = 0.f; }
@@ -255,7 +339,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
             for (int ks = 0; ks < 16; ks++) {
                 uint32_t af[4], bfr[4];
                 ldsm_x4(sQ + swz((lane & 7) + 8 * ((lane >> 3) & 1), 2 * ks + (lane >> 4)), af);
-                ldsm_x4(tK + swz(kg * KPW + (lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1)), bfr);
+                ldsm_x4(tK + kvoff(kg * KPW + (lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1)), bfr);
                 mma_bf16(sc2[0], af, bfr[0], bfr[1]);
                 mma_bf16(sc2[1], af, bfr[2], bfr[3]);
             }
@@ -310,22 +394,27 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
 #pragma unroll
             for (int nb = 0; nb < 8; nb++) {
                 uint32_t vf[4];
-                ldsm_x4_t(tV + swz(kg * KPW + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * (8 * dh + nb) + (lane >> 4)), vf);
+                ldsm_x4_t(tV + kvoff(kg * KPW + (lane & 7) + 8 * ((lane >> 3) & 1), 2 * (8 * dh + nb) + (lane >> 4)), vf);
                 mma_bf16(o[2 * nb], pf, vf[0], vf[1]);
                 mma_bf16(o[2 * nb + 1], pf, vf[2], vf[3]);
-#ifndef ATT_EXPERIMENT_NO_LO
                 mma_bf16(o[2 * nb], pl, vf[0], vf[1]);
                 mma_bf16(o[2 * nb + 1], pl, vf[2], vf[3]);
-#endif
             }
         }
-        // this tile's row offsets were consumed two iterations ago: plan tile t+3 into the same slot; the barrier below orders
-        // the plan before the load at the top of iteration t+1
-        if (t + ATT_STAGES < ntiles) plan_tile(t + ATT_STAGES, stage);
-        __syncthreads();
+        if (!TMA) {
+            // this tile's row offsets were consumed two iterations ago: plan tile t+3 into the same slot; the barrier below orders
+            // the plan before the load at the top of iteration t+1
+            if (t + ATT_STAGES < ntiles) plan_tile(t + ATT_STAGES, stage);
+            __syncthreads();
+        } else {
+            __syncwarp();
+            if (lane == 0) sm100::mbar_arrive(rbar(ATT_STAGES + stage));       // this warp has finished reading the stage
+            ring_n++;
+        }
     }
-    cp_async_wait<0>();
-    __syncthreads();
+    if (!TMA) cp_async_wait<0>();
+    if (TMA && !ring_ok && tid == 0) atomicExch(a.status, 2);
+    csync();
 
     // ---- merge the four key groups (each saw a different quarter of every tile) through shared memory ----
     float* mO = reinterpret_cast<float*>(smem + 16 * ROWB);              // [4][16][256]
@@ -345,7 +434,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
         mML[(kg * 16 + g) * 2] = m_run[0]; mML[(kg * 16 + g) * 2 + 1] = l_run[0];
         mML[(kg * 16 + g + 8) * 2] = m_run[1]; mML[(kg * 16 + g + 8) * 2 + 1] = l_run[1];
     }
-    __syncthreads();
+    csync();
     const int* pbase = meta_base(a.meta, P);
     const int nsp = pbase[pair + 1] - pbase[pair];                   // blocks that share this pair
     float* part = a.part + (size_t)slot * PART_STRIDE;
@@ -373,16 +462,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
         // the block that writes the last partial of a pair merges them (the counters were zeroed by this call's plan kernel)
         __shared__ int s_last;
         __threadfence();
-        __syncthreads();
+        csync();
         if (tid == 0) s_last = atomicAdd(meta_count(a.meta, P) + pair, 1) == nsp - 1;
-        __syncthreads();
+        csync();
         if (s_last) {
             __threadfence();
             const float* pb = a.part + (size_t)pbase[pair] * PART_STRIDE;
             // weights of every (row, partial) first (the staging memory is free here), then 16 independent accumulators per thread
             float* wsm = mO;                                             // [nsp][16] weights, then [16] 1 / sum
             for (int i = tid; i < nsp * 16; i += ATT_THREADS) wsm[i] = __ldcg(pb + (size_t)(i >> 4) * PART_STRIDE + 16 * ATT_D + 2 * (i & 15));
-            __syncthreads();
+            csync();
             if (tid < 16) {
                 float ms = -INFINITY, lsum = 0.f;
                 for (int sp = 0; sp < nsp; sp++) ms = fmaxf(ms, wsm[sp * 16 + tid]);
@@ -394,7 +483,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
                 }
                 wsm[nsp * 16 + tid] = lsum == 0.f ? 1.f : 1.f / lsum;   // sum == 0 guard as qwen35/batch.py:216
             }
-            __syncthreads();
+            csync();
             float acc[16];
 #pragma unroll
             for (int r = 0; r < 16; r++) acc[r] = 0.f;
@@ -409,11 +498,34 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) gqa_decode_split_kernel(const 
                 if (r < 4 * M) out_pair[((size_t)(r >> 2) * ATT_H + (r & 3)) * ATT_D + tid] = __float2bfloat16_rn(acc[r] * wsm[nsp * 16 + r]);
         }
     }
-    __syncthreads();                                                 // shared memory is reused by the block's next pair
+    csync();                                                         // shared memory is reused by the block's next pair
+    if (TMA) { __syncwarp(); if (lane == 0) sm100::mbar_arrive(rbar(2 * ATT_STAGES)); }       // the producer may refill the ring
   }
 }
 
 // ---- host side ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// pages [n_pages, 2, page_size, 256] bf16 as a 4-D tensor (256, page_size, 2, n_pages); box = 64 dims x 64 keys, 128-byte swizzle
+static bool make_page_map(CUtensorMap* m, const void* base, int page_size, int n_pages) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        cudaDriverEntryPointQueryResult qr;
+        void* p = nullptr;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess || qr != cudaDriverEntryPointSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    const cuuint64_t dims[4] = {(cuuint64_t)ATT_D, (cuuint64_t)page_size, (cuuint64_t)ATT_KV, (cuuint64_t)n_pages};
+    const cuuint64_t strides[3] = {(cuuint64_t)ROWB, (cuuint64_t)page_size * ROWB, (cuuint64_t)ATT_KV * page_size * ROWB};
+    const cuuint32_t box[4] = {64, 64, 1, 1}, es[4] = {1, 1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 static int sm_count() {
     static int sms[64] = {};
     int dev = 0;
@@ -450,14 +562,21 @@ static int launch_with_workspace(AttnArgs a, void* ws, size_t ws_bytes, const ch
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(gqa_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(gqa_decode_split_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(gqa_decode_split_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM) != cudaSuccess)
             return check_launch("gqa_decode smem attribute");
         attr_set[dev] = true;
     }
     gqa_decode_plan_kernel<<<1, 256, 0, stream>>>(a);
     int rc = check_launch("gqa_decode_plan");
     if (rc) return rc;
-    gqa_decode_split_kernel<<<a.G, ATT_THREADS, ATT_SMEM, stream>>>(a);
+    // pages that hold a multiple of 64 keys: every 64-key tile lies inside one page and can be fetched by tensor-map copies
+    CUtensorMap tk, tv;
+    memset(&tk, 0, sizeof(tk));
+    memset(&tv, 0, sizeof(tv));
+    bool tma = a.page_size % TK == 0 && make_page_map(&tk, a.k_pages, a.page_size, a.n_pages) && make_page_map(&tv, a.v_pages, a.page_size, a.n_pages);
+    if (tma) gqa_decode_split_kernel<true><<<a.G, ATT_THREADS + 32, ATT_SMEM, stream>>>(a, tk, tv);
+    else     gqa_decode_split_kernel<false><<<a.G, ATT_THREADS, ATT_SMEM, stream>>>(a, tk, tv);
     return check_launch("gqa_decode_split");
 }
 
