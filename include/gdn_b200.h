@@ -41,8 +41,14 @@ int gdn_version(void);
 /* Message of the last error returned to the calling thread ("" if none). */
 const char* gdn_last_error_string(void);
 
-/* Reads (and clears) the current device's status word: 0 = all device-side index checks passed since the last call,
- * 1 = some kernel skipped a row because a slot / snapshot / page index was out of range.  Synchronises the device. */
+/* Reads (and clears) the current device's status word.  Synchronises the device.  Values (the last event wins):
+ *   0  every device-side check passed since the last call
+ *   1  a slot / snapshot / page index or a cu_seqlens entry was out of range: that row (sequence) was skipped, or, for a page
+ *      index inside a context, page 0 was read in its place and that sequence's attention output is undefined
+ *   2  a bounded wait inside the decode or attention kernel gave up (its copies never arrived); the block left early
+ *   3  a bounded wait inside a prefill kernel gave up; the block left early
+ *   4  a kernel found its dynamic shared memory not 1024-byte aligned and did nothing
+ * None of these faults the device: the context stays usable and the affected outputs are left unwritten or undefined. */
 int gdn_device_status(int* status_host);
 
 /* compute_g and beta = sigmoid(b) with the reference's bf16 rounding points.
@@ -114,8 +120,7 @@ size_t gqa_decode_workspace_bytes(int B, int max_ctx);
  * page_size = Lmax, max_pages = 1, block_table = slots.
  *   q bf16 [B*M,8,256] (normed + roped, unscaled);  k_new, v_new bf16 [B*M,2,256]
  *   k_pages, v_pages bf16 [n_pages,2,page_size,256];  block_table int32 [B,max_pages];  ctx_len int32 [B] (tokens cached)
- *   out bf16 [B*M,8,256];  workspace: gqa_decode_workspace_bytes(B, max_ctx) bytes, 16-byte aligned (a smaller one is served
- *   with fewer blocks as long as it holds the plan and 2 B + 1 partials)
+ *   out bf16 [B*M,8,256];  workspace: at least gqa_decode_workspace_bytes(B, max_ctx) bytes, 16-byte aligned (GDN_E_SHAPE otherwise)
  *   max_ctx: host-side upper bound of ctx_len (informational: the work split is derived from ctx_len on the device) */
 int gqa_decode_paged(const void* q, const void* k_new, const void* v_new, void* k_pages, void* v_pages, const int* block_table,
                      const int* ctx_len, void* out, void* workspace, size_t workspace_bytes, int B, int M, int page_size,

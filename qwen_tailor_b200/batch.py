@@ -20,15 +20,20 @@ from .kernels import _rows
 HV, DK, DV, CD, PW = 16, 128, 128, 6144, 8224
 
 
-def deltanet_b(proj, conv_pool, conv_w, A_log, dt_bias, ssm_pool, slots, pos):
+def deltanet_b(proj, conv_pool, conv_w, A_log, dt_bias, ssm_pool, slots, pos, out=None):
     """proj [B, 8224] bf16; slots / pos int32 [B] (pos = tokens already in the slot's state).  Returns y [B, 2048] bf16 and updates
-    ssm_pool[slot] and the conv buffer (pos&1)^1 of the slot IN PLACE (batch.py:128-135)."""
+    ssm_pool[slot] and the conv buffer (pos&1)^1 of the slot IN PLACE (batch.py:128-135).  ``out`` (optional, additive): a
+    contiguous bf16 [B, 2048] tensor that receives y instead of a fresh one."""
     _lib.require_cuda(proj, conv_pool, conv_w, ssm_pool, slots, pos)
     proj, stride = _rows(proj)
     B = proj.shape[0]
     assert ssm_pool.dtype == torch.float32 and ssm_pool.is_contiguous() and conv_pool.dtype == torch.bfloat16 and conv_pool.is_contiguous()
     assert slots.dtype == torch.int32 and pos.dtype == torch.int32 and slots.numel() == B and pos.numel() == B
-    y = torch.empty((B, HV * DV), dtype=torch.bfloat16, device=proj.device)
+    if out is None:
+        y = torch.empty((B, HV * DV), dtype=torch.bfloat16, device=proj.device)
+    else:
+        assert out.dtype == torch.bfloat16 and out.is_contiguous() and tuple(out.shape) == (B, HV * DV) and out.device == proj.device
+        y = out
     cw = conv_w.to(torch.bfloat16).reshape(-1).contiguous()
     check(_lib.load().gdn_deltanet_b(ptr(proj), stride, ptr(conv_pool), ptr(cw), ptr(_f32(A_log)), ptr(_f32(dt_bias)), ptr(ssm_pool),
                                      ptr(slots), ptr(pos), ssm_pool.shape[0], ptr(y), B, stream_ptr(proj.device)), "deltanet_b")

@@ -194,7 +194,7 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (tid == 0) {
         mbar_init(bar(B_KQV0), 1); mbar_init(bar(B_KQV1), 1);
         mbar_init(bar(B_INPUTS), 4); mbar_init(bar(B_TB), 4); mbar_init(bar(B_AGRP), 4);
-        mbar_init(bar(B_GFREE), 2); mbar_init(bar(B_AREADY), 2); mbar_init(bar(B_YFREE), 4);
+        mbar_init(bar(B_GFREE), 4); mbar_init(bar(B_AREADY), 2); mbar_init(bar(B_YFREE), 4);
         mbar_init(bar(B_SREADY), 8); mbar_init(bar(B_ZREADY), 8); mbar_init(bar(B_DPREADY), 8); mbar_init(bar(B_YSCALED), 8);
         mbar_init(bar(B_GDONE), 1); mbar_init(bar(B_P1DONE), 1); mbar_init(bar(B_DDONE), 1); mbar_init(bar(B_SDONE), 1); mbar_init(bar(B_YDONE), 1);
         s_abort = 0;
@@ -630,6 +630,10 @@ gdn_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 fence_proxy_async_smem();
                 tc_fence_before_sync();
                 warp_arrive(B_AREADY);
+                warp_arrive(B_GFREE);
+            } else {
+                // every warp that waits on B_GDONE must have seen phase c before phase c + 1 may complete: a warp that falls a
+                // whole phase behind would mistake phase c + 2 for phase c (the parity repeats) and the block would stall
                 warp_arrive(B_GFREE);
             }
             // ---- y[t0 + i, h, v] = Y^T[v][i]: each lane owns one value row, a warp store covers 64 contiguous bytes ----

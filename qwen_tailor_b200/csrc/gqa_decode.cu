@@ -71,7 +71,7 @@ __device__ __forceinline__ uint32_t swz_t(int r, int c) { return (uint32_t)((c >
 // ---- work plan in the workspace: ints meta[0] = total tiles, meta[1] = working blocks, then cum[P+1] (tile prefix sums per (sequence, kv head) pair),
 //      base[P+1] (partial-slot prefix sums), first[P] (first block of each pair), count[P] (arrival counters, zeroed by the plan
 //      kernel of every call); the fp32 partials follow ----
-__host__ __device__ __forceinline__ size_t meta_ints(int P) { return ((size_t)(4 + 4 * (P + 1)) + 63) / 64 * 64; }
+__host__ __device__ constexpr size_t meta_ints(int P) { return ((size_t)(4 + 4 * (P + 1)) + 63) / 64 * 64; }
 __device__ __forceinline__ int* meta_cum(int* meta) { return meta + 4; }
 __device__ __forceinline__ int* meta_base(int* meta, int P) { return meta + 4 + (P + 1); }
 __device__ __forceinline__ int* meta_first(int* meta, int P) { return meta + 4 + 2 * (P + 1); }
@@ -158,6 +158,8 @@ gqa_decode_split_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm
     uint32_t ring_n = 0;                                             // tiles this block has put through the ring so far (TMA path)
     uint32_t pairs_done = 0;
     if (TMA) {
+        // the 128-byte-swizzled boxes start 16 * ROWB = 8 KiB into the dynamic shared memory: its base must be 1024-byte aligned
+        if (smem_u32(smem) & 1023u) { if (tid == 0) atomicExch(a.status, 4); return; }
         if (tid == 0) {
             for (int i = 0; i < ATT_STAGES; i++) { sm100::mbar_init(rbar(i), 1); sm100::mbar_init(rbar(ATT_STAGES + i), 8); }
             sm100::mbar_init(rbar(2 * ATT_STAGES), 8);
@@ -227,6 +229,7 @@ gqa_decode_split_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm
                     *reinterpret_cast<uint4*>(smem + 16 * ROWB + stage * 2 * TILE_BYTES + swz_t(r, c)) = kv4;
                     *reinterpret_cast<uint4*>(smem + 16 * ROWB + stage * 2 * TILE_BYTES + TILE_BYTES + swz_t(r, c)) = vv4;
                 }
+                sm100::fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) sm100::mbar_arrive(rbar(stage));
             }
@@ -262,8 +265,10 @@ gqa_decode_split_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm
             if (t < ctx_tiles) {
                 const int key = k_begin + t * TK + tid;
                 if (key < k_end) {
-                    const int page = table[key / a.page_size];
-                    if (page >= 0 && page < a.n_pages) off = (((long long)page * ATT_KV + kvh) * a.page_size + key % a.page_size) * ATT_D;
+                    int page = table[key / a.page_size];
+                    // a corrupt table entry is reported and page 0 is read in its place (in bounds; that sequence's output is undefined)
+                    if (page < 0 || page >= a.n_pages) { atomicExch(a.status, 1); page = 0; }
+                    off = (((long long)page * ATT_KV + kvh) * a.page_size + key % a.page_size) * ATT_D;
                 }
             } else if (tid < M) {
                 off = -2 - ((((long long)b * M + tid) * ATT_KV + kvh) * ATT_D);          // new rows live in k_new / v_new
@@ -330,6 +335,7 @@ gqa_decode_split_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm
                 // holds there and must not reach the MMA (0 x NaN); both warps of the key group write the same zeros
                 for (int i = lane; i < (kg * KPW + KPW - limit) * 32; i += 32)
                     *reinterpret_cast<uint4*>(smem + 16 * ROWB + stage * 2 * TILE_BYTES + TILE_BYTES + swz_t(limit + (i >> 5), i & 31)) = make_uint4(0, 0, 0, 0);
+                sm100::fence_proxy_async_smem();                     // these generic writes precede the next tensor-map copy into the stage
                 __syncwarp();
             }
             float sc2[2][4];
@@ -498,6 +504,7 @@ gqa_decode_split_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm
                 if (r < 4 * M) out_pair[((size_t)(r >> 2) * ATT_H + (r & 3)) * ATT_D + tid] = __float2bfloat16_rn(acc[r] * wsm[nsp * 16 + r]);
         }
     }
+    if (TMA) sm100::fence_proxy_async_smem();                        // merge scratch was written through the generic proxy
     csync();                                                         // shared memory is reused by the block's next pair
     if (TMA) { __syncwarp(); if (lane == 0) sm100::mbar_arrive(rbar(2 * ATT_STAGES)); }       // the producer may refill the ring
   }
@@ -594,7 +601,8 @@ int launch_gqa_decode(AttnArgs a, void* workspace, size_t workspace_bytes, cudaS
 // ----------------------------------------------------------------------------------------------------------------------
 constexpr int STATIC_PARTIALS = 762;                                   // partial slots that fit next to the plan
 constexpr int STATIC_MAX_B = 256;                                      // sequences per call: 2 * 256 pairs + one block per SM <= 762
-static __device__ __align__(256) float g_static_scratch[(size_t)STATIC_PARTIALS * PART_STRIDE + 2048];      // 12 MiB
+constexpr size_t STATIC_SCRATCH_FLOATS = (size_t)STATIC_PARTIALS * PART_STRIDE + meta_ints(2 * STATIC_MAX_B);      // partials + the plan of 512 pairs
+static __device__ __align__(256) float g_static_scratch[STATIC_SCRATCH_FLOATS];                                    // 12 MiB
 
 int launch_gqa_decode_static(AttnArgs a, cudaStream_t stream) {
     if (a.B <= 0) return GDN_OK;
@@ -618,7 +626,7 @@ int launch_gqa_decode_static(AttnArgs a, cudaStream_t stream) {
         }
         addr[dev] = p;
     }
-    return launch_with_workspace(a, addr[dev], sizeof(float) * ((size_t)STATIC_PARTIALS * PART_STRIDE + 2048), "gqa_decode_paged_static", stream);
+    return launch_with_workspace(a, addr[dev], sizeof(float) * STATIC_SCRATCH_FLOATS, "gqa_decode_paged_static", stream);
 }
 
 }  // namespace gdn
