@@ -71,20 +71,49 @@ int gdn_normalize_qk(const void* q, const void* k, void* q_out, void* k_out, lon
 int gdn_recurrent(const void* q, const void* k, const void* v, const float* g, const float* beta, const float* state_in, void* y,
                   float* state_out, int B, int T, int Hk, int Hv, int Dk, int Dv, void* stream);
 
-/* Chunked prefill (chunk 64, tcgen05 tensor cores) over a packed varlen batch, with optional resume from a cached state.
- * Replaces: gdn_chunked, qwen35/gdn_nax.py:413-426 (phase A :71-143, phase B :224-358).  The reference handles one sequence
- * per call (B = 1); cu_seqlens packing and init_idx are the additive extension for ragged batches and prefix-cache resume.
+/* Chunked prefill (chunk 64, tcgen05 tensor cores) over a packed varlen batch, with optional resume from a cached state:
+ * phase A followed by phase B (the two entry points below), as the reference's gdn_chunked is its two kernels back to back.
+ * Replaces: gdn_chunked, qwen35/gdn_nax.py:413-426.  The reference handles one sequence per call (B = 1); cu_seqlens packing
+ * and init_idx are the additive extension for ragged batches and prefix-cache resume.
  *   q, k, v  bf16 [total_T, H, 128] (q, k already normalised; q scaled by 128^-1/2), 16-byte aligned
  *   lg, beta fp32 [total_T, H]: log-decay and beta of every token and head (see gdn_gates)
  *   cu_seqlens int32 [n_seq+1] (device): sequence s owns tokens [cu_seqlens[s], cu_seqlens[s+1])
  *   init_state fp32 [*, H, 128, 128] or NULL (zero states); init_idx int32 [n_seq] (device) or NULL: row of init_state the
  *              sequence resumes from, negative = zero state; with init_state != NULL and init_idx == NULL row s is used
  *   y bf16 [total_T, H, 128];  final_state fp32 [n_seq, H, 128, 128]
+ *   workspace: gdn_prefill_workspace_bytes(n_seq, total_T, H) bytes, 16-byte aligned: the phase-A records between the two kernels
  *   heads [head_lo, head_hi) are computed (head-group sharding of one long sequence); the others are not touched
- * Errors: GDN_E_SHAPE for bad sizes, GDN_E_ALIGN, GDN_E_UNSUPPORTED if the driver lacks tensor-map support. */
+ * Errors: GDN_E_SHAPE for bad sizes or a short workspace, GDN_E_ALIGN, GDN_E_UNSUPPORTED if the driver lacks tensor-map support. */
 int gdn_prefill_chunked(const void* q, const void* k, const void* v, const float* lg, const float* beta, const int* cu_seqlens,
-                        const float* init_state, const int* init_idx, void* y, float* final_state, int n_seq, long long total_T, int H,
-                        int head_lo, int head_hi, void* stream);
+                        const float* init_state, const int* init_idx, void* y, float* final_state, void* workspace, size_t workspace_bytes,
+                        int n_seq, long long total_T, int H, int head_lo, int head_hi, void* stream);
+
+/* Bytes of the phase-A record buffer for a packed batch: (total_T / 64 + n_seq) * H records of 17,152 bytes (Tb as bf16 hi + lo
+ * operand images, and the chunk's cumulative log-decay, gamma and dec vectors).  Stands in for the reference's Tbuf / Abuf / gv
+ * outputs of phase A (qwen35/gdn_nax.py:394-401,420-422). */
+size_t gdn_prefill_workspace_bytes(int n_seq, long long total_T, int H);
+
+/* Phase A: the state-independent part of every 64-token chunk, one independent tile per (chunk, head) -- cumulative decay,
+ * K K^T on the tensor cores, the exact inverse (I + L)^-1 and Tb = T diag(beta) -- written as records for phase B.
+ * Replaces: the reference's phase-A kernel gdn_nax_a, qwen35/gdn_nax.py:71-143 (launched at :420-422). */
+int gdn_phase_a(const void* k, const float* lg, const float* beta, const int* cu_seqlens, void* records, size_t records_bytes, int n_seq,
+                long long total_T, int H, int head_lo, int head_hi, void* stream);
+
+/* Phase A fused with the prefill front end: reads the in_proj rows once, computes conv (4 taps) + silu, q / k l2norm (q also scaled
+ * by 128^-1/2) and the gates, writes q, k, v for phase B and the phase-A records.  Bit-identical to gdn_conv_prep + gdn_gates +
+ * gdn_phase_a.  H is 16 (the in_proj row layout fixes it).
+ * Replaces: prep_a, qwen35/gdn_nax.py:394-401 (kernel :150-222), the reference's default prefill path (qwen35/prefill.py:251-252).
+ *   proj bf16 [total_T, row_stride >= 8224];  conv_state bf16 [n_seq, 3, 6144]: the three raw rows before each sequence
+ *   conv_w bf16 [6144*4];  A_log, dt_bias fp32 [16];  q, k, v bf16 [total_T, 16, 128] outputs */
+int gdn_prep_a(const void* proj, long long row_stride, const void* conv_state, const void* conv_w, const float* A_log, const float* dt_bias,
+               const int* cu_seqlens, void* q, void* k, void* v, void* records, size_t records_bytes, int n_seq, long long total_T, int head_lo,
+               int head_hi, void* stream);
+
+/* Phase B: the serial chain over the chunks of every (sequence, head), fp32 state resident in tensor memory.
+ * Replaces: phase_b, qwen35/gdn_nax.py:404-410 (kernel gdn_nax_b :224-358), called at qwen35/prefill.py:253. */
+int gdn_phase_b(const void* q, const void* k, const void* v, const void* records, size_t records_bytes, const int* cu_seqlens,
+                const float* init_state, const int* init_idx, void* y, float* final_state, int n_seq, long long total_T, int H, int head_lo,
+                int head_hi, void* stream);
 
 /* Decode / speculative verify, solo flavour: M chained tokens, functional snapshot outputs.
  * Replaces: deltanet, qwen35/kernels.py:555-567 (kernel :461-552).

@@ -28,7 +28,11 @@ SIGNATURES = {
     "gdn_gates": (I, [P, P, LL, LL, P, P, P, P, P, LL, I, P]),
     "gdn_normalize_qk": (I, [P, P, P, P, LL, F, F, P]),
     "gdn_recurrent": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
-    "gdn_prefill_chunked": (I, [P, P, P, P, P, P, P, P, P, P, I, LL, I, I, I, P]),
+    "gdn_prefill_chunked": (I, [P, P, P, P, P, P, P, P, P, P, P, SZ, I, LL, I, I, I, P]),
+    "gdn_prefill_workspace_bytes": (SZ, [I, LL, I]),
+    "gdn_phase_a": (I, [P, P, P, P, P, SZ, I, LL, I, I, I, P]),
+    "gdn_prep_a": (I, [P, LL, P, P, P, P, P, P, P, P, P, SZ, I, LL, I, I, P]),
+    "gdn_phase_b": (I, [P, P, P, P, SZ, P, P, P, P, P, I, LL, I, I, I, P]),
     "gdn_deltanet": (I, [P, LL, P, P, P, P, P, P, I, P, P, P, I, P]),
     "gdn_deltanet_b": (I, [P, LL, P, P, P, P, P, P, P, I, P, I, P]),
     "gdn_deltanet_bm": (I, [P, LL, P, P, P, P, P, P, P, P, I, P, I, I, P]),

@@ -93,26 +93,87 @@ int gdn_recurrent(const void* q, const void* k, const void* v, const float* g, c
     return launch_recurrent(a, static_cast<cudaStream_t>(stream));
 }
 
-int gdn_prefill_chunked(const void* q, const void* k, const void* v, const float* lg, const float* beta, const int* cu_seqlens,
-                        const float* init_state, const int* init_idx, void* y, float* final_state, int n_seq, long long total_T, int H,
-                        int head_lo, int head_hi, void* stream) {
-    REQUIRE(q && k && v && lg && beta && cu_seqlens && y && final_state, GDN_E_NULL, "gdn_prefill_chunked: null pointer");
-    REQUIRE(n_seq >= 0 && total_T >= 0 && total_T < (1ll << 31) && H > 0 && H <= 65535, GDN_E_SHAPE, "gdn_prefill_chunked: n_seq=%d total_T=%lld H=%d",
-            n_seq, total_T, H);
-    REQUIRE(head_lo >= 0 && head_lo <= head_hi && head_hi <= H, GDN_E_SHAPE, "gdn_prefill_chunked: head range [%d, %d) outside [0, %d)", head_lo,
-            head_hi, H);
-    REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(init_state) && aligned16(final_state), GDN_E_ALIGN,
-            "gdn_prefill_chunked: q / k / v / states must be 16-byte aligned");
-    if (n_seq == 0 || head_lo == head_hi) return GDN_OK;
-    PrefillArgs a{};
-    a.lg = lg; a.beta = beta; a.cu_seqlens = cu_seqlens; a.init_state = init_state; a.init_idx = init_idx;
-    a.y = static_cast<__nv_bfloat16*>(y); a.final_state = final_state;
+size_t gdn_prefill_workspace_bytes(int n_seq, long long total_T, int H) {
+    if (n_seq <= 0 || total_T < 0 || H <= 0) return 0;
+    return prefill_records_bytes(n_seq, total_T, H);
+}
+
+static int prefill_common(const char* who, const int* cu_seqlens, const void* records, size_t records_bytes, int n_seq, long long total_T, int H,
+                          int head_lo, int head_hi) {
+    REQUIRE(cu_seqlens && records, GDN_E_NULL, "%s: null pointer", who);
+    REQUIRE(n_seq >= 0 && total_T >= 0 && total_T < (1ll << 31) && H > 0 && H <= 65535, GDN_E_SHAPE, "%s: n_seq=%d total_T=%lld H=%d", who, n_seq,
+            total_T, H);
+    REQUIRE(head_lo >= 0 && head_lo <= head_hi && head_hi <= H, GDN_E_SHAPE, "%s: head range [%d, %d) outside [0, %d)", who, head_lo, head_hi, H);
+    REQUIRE(aligned16(records), GDN_E_ALIGN, "%s: the record buffer must be 16-byte aligned", who);
+    REQUIRE(records_bytes >= prefill_records_bytes(n_seq, total_T, H), GDN_E_SHAPE, "%s: record buffer of %zu bytes < %zu (gdn_prefill_workspace_bytes)",
+            who, records_bytes, prefill_records_bytes(n_seq, total_T, H));
+    return GDN_OK;
+}
+
+int gdn_phase_a(const void* k, const float* lg, const float* beta, const int* cu_seqlens, void* records, size_t records_bytes, int n_seq,
+                long long total_T, int H, int head_lo, int head_hi, void* stream) {
+    REQUIRE(k && lg && beta, GDN_E_NULL, "gdn_phase_a: null pointer");
+    int rc = prefill_common("gdn_phase_a", cu_seqlens, records, records_bytes, n_seq, total_T, H, head_lo, head_hi);
+    if (rc) return rc;
+    REQUIRE(aligned16(k), GDN_E_ALIGN, "gdn_phase_a: k must be 16-byte aligned");
+    if (n_seq == 0 || head_lo == head_hi || total_T == 0) return GDN_OK;
+    PhaseAArgs a{};
+    a.lg = lg; a.beta = beta; a.cu_seqlens = cu_seqlens; a.records = static_cast<unsigned char*>(records);
     a.n_seq = n_seq; a.H = H; a.head_lo = head_lo; a.n_heads = head_hi - head_lo; a.total_T = total_T;
     a.status = status_ptr();
-    REQUIRE(a.status, GDN_E_LAUNCH, "gdn_prefill_chunked: no CUDA device");
-    if (total_T == 0) total_T = 1;          // a tensor map needs a non-empty extent; empty sequences never issue a copy
-    a.total_T = total_T;
-    return launch_prefill(q, k, v, a, static_cast<cudaStream_t>(stream));
+    REQUIRE(a.status, GDN_E_LAUNCH, "gdn_phase_a: no CUDA device");
+    return launch_phase_a(k, a, false, static_cast<cudaStream_t>(stream));
+}
+
+int gdn_prep_a(const void* proj, long long row_stride, const void* conv_state, const void* conv_w, const float* A_log, const float* dt_bias,
+               const int* cu_seqlens, void* q, void* k, void* v, void* records, size_t records_bytes, int n_seq, long long total_T, int head_lo,
+               int head_hi, void* stream) {
+    REQUIRE(proj && conv_state && conv_w && A_log && dt_bias && q && k && v, GDN_E_NULL, "gdn_prep_a: null pointer");
+    int rc = prefill_common("gdn_prep_a", cu_seqlens, records, records_bytes, n_seq, total_T, HV, head_lo, head_hi);
+    if (rc) return rc;
+    REQUIRE(row_stride >= PW && row_stride % 4 == 0, GDN_E_SHAPE, "gdn_prep_a: proj row stride %lld (need >= 8224 and a multiple of 4)", row_stride);
+    REQUIRE(((uintptr_t)proj | (uintptr_t)conv_state | (uintptr_t)conv_w | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v) % 8 == 0, GDN_E_ALIGN,
+            "gdn_prep_a: tensors must be 8-byte aligned");
+    if (n_seq == 0 || head_lo == head_hi || total_T == 0) return GDN_OK;
+    PhaseAArgs a{};
+    a.cu_seqlens = cu_seqlens; a.records = static_cast<unsigned char*>(records);
+    a.n_seq = n_seq; a.H = HV; a.head_lo = head_lo; a.n_heads = head_hi - head_lo; a.total_T = total_T;
+    a.proj = static_cast<const __nv_bfloat16*>(proj); a.row_stride = row_stride;
+    a.conv_state = static_cast<const __nv_bfloat16*>(conv_state); a.conv_w = static_cast<const __nv_bfloat16*>(conv_w);
+    a.A_log = A_log; a.dt_bias = dt_bias;
+    a.q = static_cast<__nv_bfloat16*>(q); a.k = static_cast<__nv_bfloat16*>(k); a.v = static_cast<__nv_bfloat16*>(v);
+    a.status = status_ptr();
+    REQUIRE(a.status, GDN_E_LAUNCH, "gdn_prep_a: no CUDA device");
+    return launch_phase_a(nullptr, a, true, static_cast<cudaStream_t>(stream));
+}
+
+int gdn_phase_b(const void* q, const void* k, const void* v, const void* records, size_t records_bytes, const int* cu_seqlens,
+                const float* init_state, const int* init_idx, void* y, float* final_state, int n_seq, long long total_T, int H, int head_lo,
+                int head_hi, void* stream) {
+    REQUIRE(q && k && v && y && final_state, GDN_E_NULL, "gdn_phase_b: null pointer");
+    int rc = prefill_common("gdn_phase_b", cu_seqlens, records, records_bytes, n_seq, total_T, H, head_lo, head_hi);
+    if (rc) return rc;
+    REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(init_state) && aligned16(final_state), GDN_E_ALIGN,
+            "gdn_phase_b: q / k / v / states must be 16-byte aligned");
+    if (n_seq == 0 || head_lo == head_hi) return GDN_OK;
+    PrefillArgs a{};
+    a.records = static_cast<const unsigned char*>(records);
+    a.cu_seqlens = cu_seqlens; a.init_state = init_state; a.init_idx = init_idx;
+    a.y = static_cast<__nv_bfloat16*>(y); a.final_state = final_state;
+    a.n_seq = n_seq; a.H = H; a.head_lo = head_lo; a.n_heads = head_hi - head_lo;
+    a.status = status_ptr();
+    REQUIRE(a.status, GDN_E_LAUNCH, "gdn_phase_b: no CUDA device");
+    a.total_T = total_T == 0 ? 1 : total_T;     // a tensor map needs a non-empty extent; empty sequences never issue a copy
+    return launch_phase_b(q, k, v, a, static_cast<cudaStream_t>(stream));
+}
+
+int gdn_prefill_chunked(const void* q, const void* k, const void* v, const float* lg, const float* beta, const int* cu_seqlens,
+                        const float* init_state, const int* init_idx, void* y, float* final_state, void* workspace, size_t workspace_bytes,
+                        int n_seq, long long total_T, int H, int head_lo, int head_hi, void* stream) {
+    int rc = gdn_phase_a(k, lg, beta, cu_seqlens, workspace, workspace_bytes, n_seq, total_T, H, head_lo, head_hi, stream);
+    if (rc) return rc;
+    return gdn_phase_b(q, k, v, workspace, workspace_bytes, cu_seqlens, init_state, init_idx, y, final_state, n_seq, total_T, H, head_lo, head_hi,
+                       stream);
 }
 
 static int decode_common(DecodeArgs& a, void* stream, const char* who) {

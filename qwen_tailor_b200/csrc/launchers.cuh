@@ -59,10 +59,32 @@ size_t gqa_workspace_bytes(int B, int max_ctx);
 int launch_gqa_decode(AttnArgs a, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 int launch_gqa_decode_static(AttnArgs a, cudaStream_t stream);
 
-// ---- gdn_prefill_sm100.cu ----
-struct PrefillArgs {
-    const float* lg;                  // [total_T, H] log-decay per token and head
+// ---- gdn_phase_a.cu / gdn_prefill_sm100.cu ----
+constexpr int PA_REC_BYTES = 17152;   // one phase-A record: Tb hi + Tb lo (2 x 8 KiB operand images) + Lc, gamma, dec ([64] fp32 each)
+
+struct PhaseAArgs {
+    const float* lg;                  // [total_T, H] log-decay per token and head            (plain flavour)
     const float* beta;                // [total_T, H]
+    const int* cu_seqlens;            // [n_seq + 1]
+    unsigned char* records;           // [total_T / 64 + n_seq][H] records of PA_REC_BYTES
+    int* status;
+    int n_seq, H, head_lo, n_heads;
+    long long total_T;
+    // fused flavour: q, k, v, the gates and the records all come from the in_proj rows
+    const __nv_bfloat16* proj;        // [total_T, row_stride] rows: qkv 6144 | z 2048 | b 16 | a 16
+    long long row_stride;
+    const __nv_bfloat16* conv_state;  // [n_seq, 3, 6144] raw rows before each sequence
+    const __nv_bfloat16* conv_w;      // [6144*4]
+    const float* A_log;               // [16]
+    const float* dt_bias;             // [16]
+    __nv_bfloat16 *q, *k, *v;         // [total_T, 16, 128] outputs
+};
+long long phase_a_slots(int n_seq, long long total_T);
+size_t prefill_records_bytes(int n_seq, long long total_T, int H);
+int launch_phase_a(const void* k, const PhaseAArgs& a, bool fused, cudaStream_t stream);
+
+struct PrefillArgs {
+    const unsigned char* records;     // phase-A records (see PhaseAArgs)
     const int* cu_seqlens;            // [n_seq + 1] token offsets of the packed sequences
     const float* init_state;          // [*, H, 128, 128] fp32 or nullptr (all sequences start from zero)
     const int* init_idx;              // [n_seq] row of init_state per sequence (< 0 = zero state) or nullptr (row = sequence)
@@ -72,7 +94,7 @@ struct PrefillArgs {
     int n_seq, H, head_lo, n_heads;
     long long total_T;
 };
-int launch_prefill(const void* q, const void* k, const void* v, const PrefillArgs& a, cudaStream_t stream);
+int launch_phase_b(const void* q, const void* k, const void* v, const PrefillArgs& a, cudaStream_t stream);
 
 // ---- attn_glue.cu ----
 int launch_qkv_prep(const __nv_bfloat16* qkv, long long row_stride, const float* q_norm, const float* k_norm, const int* row_pos, __nv_bfloat16* q,
