@@ -27,6 +27,7 @@ int check_launch(const char* what) {
 // one status word per device, written by kernels that skip a row with a bad index
 __device__ int g_status_word;
 
+
 static int* status_ptr() {
     static int* ptrs[64] = {};
     int dev = 0;

@@ -46,6 +46,15 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Optional in-kernel time stamps (builds with -DGDN_TIMING only): block 0 logs clock64() at labelled points into the translation
+// unit's own g_tlog, which that unit's gdn_timing_log_* function copies out.
+#ifdef GDN_TIMING
+static __device__ long long g_tlog[8192];
+#define GDN_TSTAMP(slot) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (slot) < 8192) g_tlog[(slot)] = clock64(); } while (0)
+#else
+#define GDN_TSTAMP(slot) do { } while (0)
+#endif
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

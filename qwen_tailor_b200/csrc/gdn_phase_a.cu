@@ -9,10 +9,11 @@
 // of the prefill is the chain kernel in gdn_prefill_sm100.cu, which reads what this kernel writes).
 //
 // K K^T runs on the tensor cores (tcgen05.mma, fp32 accumulator in tensor memory, K fetched by one TMA tile load).  The inverse is
-// exact fp32: forward substitution on the four 16 x 16 diagonal blocks (one warp each, a 15-deep dependent chain instead of 63),
-// then the off-diagonal blocks are assembled as block products  T_ba = -T_bb (L_ba T_aa)  in fp32 FMAs -- two 16^3 product pairs
-// and one 32^3 pair.  (The reference does the same substitution per 16-token chunk, qwen35/gdn_nax.py:118-141; products of the
-// inverse blocks are what a 64-token chunk adds.)
+// fp32 throughout: exact forward substitution on the four 16 x 16 diagonal blocks (one warp each, a 15-deep dependent chain
+// instead of 63), then the off-diagonal blocks are assembled as block products  T_ba = -T_bb (L_ba T_aa)  -- two 16^3 product
+// pairs and one 32^3 pair -- on the tensor cores as well (mma.sync tf32, every fp32 operand as a two-term tf32 split with the three
+// significant partial products accumulated in fp32, so the products carry fp32-class accuracy).  The reference does the same
+// substitution per 16-token chunk (qwen35/gdn_nax.py:118-141); the products of inverse blocks are what a 64-token chunk adds.
 //
 // Output record of a tile (17,152 bytes, consumed by the chain kernel with one bulk copy):
 //     Tb as bf16 hi / lo parts, each a [64][64] K-major operand image with the 128-byte swizzle already applied  (2 x 8 KiB)
@@ -36,10 +37,10 @@ using namespace sm100;
 constexpr int PA_THREADS = 128;
 constexpr int PA_CH = 64;
 constexpr int PA_LS = 68;                                  // row stride (floats) of the fp32 L and T tiles
-constexpr int PA_SM_K = 0;                                 // K tile: two [64][64] bf16 boxes, 128-byte swizzle   (16 KiB)
-constexpr int PA_SM_L = 16384;                             // L fp32 [64][68]
-constexpr int PA_SM_T = PA_SM_L + 64 * PA_LS * 4;          // T fp32 [64][68]; its upper-right blocks are scratch for the block products
-constexpr int PA_SM_G = PA_SM_T + 64 * PA_LS * 4;          // Lc[64], beta[64]
+constexpr int PA_SM_K = 0;                                 // K tile: two [64][64] bf16 boxes, 128-byte swizzle (16 KiB); once K K^T
+constexpr int PA_SM_T = 0;                                 //   has been formed the same bytes hold T fp32 [64][68]
+constexpr int PA_SM_L = 64 * PA_LS * 4;                    // raw K K^T, then L, fp32 [64][68]; consumed blocks take the inner block products
+constexpr int PA_SM_G = 2 * 64 * PA_LS * 4;                // Lc[64], beta[64]
 constexpr int PA_SM_TOTAL = PA_SM_G + 512;
 constexpr uint32_t PA_WAIT_LIMIT = 200000u;
 
@@ -48,6 +49,61 @@ __device__ __forceinline__ float pa_ex2(float x) { float y; asm("ex2.approx.ftz.
 __device__ __forceinline__ void pa_split_pack(float x0, float x1, uint32_t& hi, uint32_t& lo) {
     hi = pack_bf16x2(x0, x1);
     lo = pack_bf16x2(x0 - __uint_as_float(hi << 16), x1 - __uint_as_float(hi & 0xffff0000u));
+}
+
+// bounded wait with a pause between polls
+__device__ __forceinline__ bool pa_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < PA_WAIT_LIMIT; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(100);
+    }
+    return false;
+}
+
+// ---- fp32 block products on the tensor cores: mma.sync m16n8k8 tf32 with each fp32 operand split into two tf32 terms and the
+//      three significant partial products accumulated in fp32 (hi hi + lo hi + hi lo: ~21 significand bits, fp32-class accuracy) ----
+// hi = x truncated to tf32 (a mask, so the conversion unit stays free for the ex2 of the L build), lo = the exact residual, again
+// truncated: hi + lo carries 21 significand bits of x
+__device__ __forceinline__ void tf32_split(float x, uint32_t& hi, uint32_t& lo) {
+    hi = __float_as_uint(x) & 0xFFFFE000u;
+    lo = __float_as_uint(x - __uint_as_float(hi)) & 0xFFFFE000u;
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+// acc[nt] (+)= A[16 x 8 KS] B[8 KS x 8 NT] for one warp: A, B row-major fp32 in shared memory (element (r, c) at p[r * ld + c]),
+// A = rows [0, 16), B columns [8 nt, 8 nt + 8).  Fragment layout of m16n8k8: g = lane / 4, t = lane % 4;
+// a = {(g, t), (g + 8, t), (g, t + 4), (g + 8, t + 4)}, b = {(t, g), (t + 4, g)}, c = {(g, 2t), (g, 2t + 1), (g + 8, 2t), (g + 8, 2t + 1)}.
+template <int KS, int NT>
+__device__ __forceinline__ void warp_mm_tf32x3(const float* __restrict__ A, int lda, const float* __restrict__ B, int ldb, int lane, float (&acc)[NT][4]) {
+    const int g = lane >> 2, t = lane & 3;
+    float lo1[NT][4], lo2[NT][4];                                     // the two small partial products keep their own accumulators:
+#pragma unroll                                                        // three independent MMA chains instead of one three times as long
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) { lo1[nt][e] = 0.f; lo2[nt][e] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+        uint32_t ah[4], al[4];
+        tf32_split(A[g * lda + 8 * ks + t], ah[0], al[0]);
+        tf32_split(A[(g + 8) * lda + 8 * ks + t], ah[1], al[1]);
+        tf32_split(A[g * lda + 8 * ks + t + 4], ah[2], al[2]);
+        tf32_split(A[(g + 8) * lda + 8 * ks + t + 4], ah[3], al[3]);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            uint32_t bh[2], bl[2];
+            tf32_split(B[(8 * ks + t) * ldb + 8 * nt + g], bh[0], bl[0]);
+            tf32_split(B[(8 * ks + t + 4) * ldb + 8 * nt + g], bh[1], bl[1]);
+            mma_tf32(lo1[nt], al, bh);
+            mma_tf32(lo2[nt], ah, bl);
+            mma_tf32(acc[nt], ah, bh);
+        }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) acc[nt][e] += lo1[nt][e] + lo2[nt][e];
 }
 
 // (sequence, chunk) of a record slot: slot = cu_seqlens[s] / 64 + s + c.  Returns false for slots that no chunk maps to.
@@ -64,7 +120,7 @@ __device__ __forceinline__ bool slot_to_chunk(const int* __restrict__ cu, int n_
 }
 
 template <bool FUSED>
-__global__ void __launch_bounds__(PA_THREADS, 4)
+__global__ void __launch_bounds__(PA_THREADS, 6)
 gdn_phase_a_kernel(const __grid_constant__ CUtensorMap tmK, const PhaseAArgs a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ uint64_t bars[2];
@@ -98,6 +154,7 @@ gdn_phase_a_kernel(const __grid_constant__ CUtensorMap tmK, const PhaseAArgs a) 
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tb = tmem_slot;
+    GDN_TSTAMP(0);
 
     float lgj = 0.f, bj = 0.f;                                       // log-decay and beta of token tid (threads 0..63)
     if (!FUSED) {
@@ -177,8 +234,10 @@ gdn_phase_a_kernel(const __grid_constant__ CUtensorMap tmK, const PhaseAArgs a) 
         for (int o = 1; o < 32; o <<= 1) { const float y = __shfl_up_sync(0xffffffffu, xs, o); if (lane >= o) xs += y; }
         if (lane == 31) s_scan[warp] = xs;
     }
-    if (!FUSED) {
-        if (!mbar_wait(bar_k, 0, PA_WAIT_LIMIT)) { atomicExch(a.status, 3); }      // every thread waits: the copy's writes become visible to it
+    // one warp polls the barrier (a poll loop costs issue slots that the five other resident blocks want); the block barrier below
+    // hands the copy's writes on to the other warps
+    if (!FUSED && warp == 0) {
+        if (!pa_wait(bar_k, 0) && lane == 0) atomicExch(a.status, 3);
     }
     // rows past the end of the sequence are zero (qwen35/gdn_nax.py:55-60): a packed neighbour sequence must not leak in
     if (nrows < PA_CH) {
@@ -191,6 +250,7 @@ gdn_phase_a_kernel(const __grid_constant__ CUtensorMap tmK, const PhaseAArgs a) 
     fence_proxy_async_smem();
     __syncthreads();
     if (warp == 1) xs += s_scan[0];
+    GDN_TSTAMP(1);
     const float Ltot = s_scan[0] + s_scan[1];
     if (tid < 64) { sLc[tid] = xs; sBeta[tid] = bj; }
 
@@ -204,130 +264,128 @@ gdn_phase_a_kernel(const __grid_constant__ CUtensorMap tmK, const PhaseAArgs a) 
         }
         mma_commit(bar_mma);
     }
-    __syncthreads();                                                 // Lc / beta visible to everyone
-    const bool mma_ok = mbar_wait(bar_mma, 0, PA_WAIT_LIMIT);
+    if (warp == 0) {
+        if (!pa_wait(bar_mma, 0) && lane == 0) atomicExch(a.status, 3);      // (a product that never completed leaves garbage, not a fault)
+    }
+    __syncthreads();                                                 // Lc / beta and the finished product are visible to everyone
     tc_fence_after_sync();
-    if (!mma_ok) atomicExch(a.status, 3);
+    GDN_TSTAMP(2);
 
-    // ---- L rows (threads 0..63 own TMEM lanes 0..63): L[i][j] = beta_i 2^(Lc_i - Lc_j) G[i][j] for j < i ----
-    if (tid < 64 && mma_ok) {
-        const int i = tid;
-        const float Li = xs, bi = bj;
+    // ---- raw K K^T rows out of tensor memory (threads 0..63 own TMEM lanes 0..63) ----
+    if (tid < 64) {
 #pragma unroll
         for (int half = 0; half < 2; half++) {
             uint32_t r[32];
             tmem_ld32(tb + ((uint32_t)(warp * 32) << 16) + half * 32, r);
             tmem_wait_ld();
 #pragma unroll
-            for (int jj = 0; jj < 32; jj += 4) {
-                const int j = half * 32 + jj;
-                const float4 lc = *reinterpret_cast<const float4*>(sLc + j);
-                float4 o;
-                o.x = (j < i) ? bi * pa_ex2(Li - lc.x) * __uint_as_float(r[jj]) : 0.f;
-                o.y = (j + 1 < i) ? bi * pa_ex2(Li - lc.y) * __uint_as_float(r[jj + 1]) : 0.f;
-                o.z = (j + 2 < i) ? bi * pa_ex2(Li - lc.z) * __uint_as_float(r[jj + 2]) : 0.f;
-                o.w = (j + 3 < i) ? bi * pa_ex2(Li - lc.w) * __uint_as_float(r[jj + 3]) : 0.f;
-                *reinterpret_cast<float4*>(Lm + i * PA_LS + j) = o;
-            }
+            for (int jj = 0; jj < 32; jj += 4)
+                *reinterpret_cast<float4*>(Lm + tid * PA_LS + half * 32 + jj) =
+                    make_float4(__uint_as_float(r[jj]), __uint_as_float(r[jj + 1]), __uint_as_float(r[jj + 2]), __uint_as_float(r[jj + 3]));
         }
     }
     tc_fence_before_sync();
     __syncthreads();
+    GDN_TSTAMP(3);
+    // ---- L[i][j] = beta_i 2^(Lc_i - Lc_j) G[i][j] for j < i, in place; thread = (row, half of the columns) ----
+    {
+        const int i = tid >> 1, hf = tid & 1;
+        const float Li = sLc[i], bi = sBeta[i];
+        float* row = Lm + i * PA_LS + hf * 32;
+#pragma unroll
+        for (int jj = 0; jj < 32; jj += 4) {
+            const int j = hf * 32 + jj;
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (j < i) {
+                const float4 g = *reinterpret_cast<const float4*>(row + jj);
+                const float4 lc = *reinterpret_cast<const float4*>(sLc + j);
+                o.x = bi * pa_ex2(Li - lc.x) * g.x;
+                o.y = (j + 1 < i) ? bi * pa_ex2(Li - lc.y) * g.y : 0.f;
+                o.z = (j + 2 < i) ? bi * pa_ex2(Li - lc.z) * g.z : 0.f;
+                o.w = (j + 3 < i) ? bi * pa_ex2(Li - lc.w) * g.w : 0.f;
+            }
+            *reinterpret_cast<float4*>(row + jj) = o;
+        }
+    }
+    __syncthreads();
 
-    // ---- T = (I + L)^-1 ----
-    // (1) diagonal blocks: warp w inverts block w; lane j < 16 owns column j:  t_i = [i == j] - sum_{m < i} L[i][m] t_m
+    // ---- T = (I + L)^-1 (T overwrites the K tile, which the tensor cores have finished reading) ----
+    // (1) diagonal blocks: warp w inverts block w; lane j < 16 owns column j:  t_i = [i == j] - sum_{m < i} L[i][m] t_m.
+    //     Lanes 16..31 of warps 0 and 2 zero the block to the right of theirs: steps (2) and (3) read whole 32 x 32 diagonal blocks.
     if (lane < 16) {
         const int b0 = warp * 16;
+        // right-looking: once t_m is final, every later row takes its contribution -- sixteen independent accumulators, so the
+        // dependent chain is one FMA per step instead of a whole row sum
         float t[16];
 #pragma unroll
-        for (int i = 0; i < 16; i++) {
-            float acc = (i == lane) ? 1.f : 0.f;
-            const float4* lrow = reinterpret_cast<const float4*>(Lm + (b0 + i) * PA_LS + b0);     // broadcast reads: every lane needs the same L entries
+        for (int i = 0; i < 16; i++) t[i] = (i == lane) ? 1.f : 0.f;
+        const float* lblk = Lm + b0 * PA_LS + b0;                     // broadcast reads: every lane needs the same L entries
 #pragma unroll
-            for (int v4 = 0; v4 < 4; v4++) {
-                if (4 * v4 < i) {
-                    const float4 l = lrow[v4];
-                    acc -= l.x * t[4 * v4];
-                    if (4 * v4 + 1 < i) acc -= l.y * t[4 * v4 + 1];
-                    if (4 * v4 + 2 < i) acc -= l.z * t[4 * v4 + 2];
-                    if (4 * v4 + 3 < i) acc -= l.w * t[4 * v4 + 3];
-                }
-            }
-            t[i] = acc;
+        for (int m = 0; m < 15; m++) {
+#pragma unroll
+            for (int i = m + 1; i < 16; i++) t[i] -= lblk[i * PA_LS + m] * t[m];
         }
 #pragma unroll
         for (int i = 0; i < 16; i++) Tm[(b0 + i) * PA_LS + b0 + lane] = t[i];
+    } else if ((warp & 1) == 0) {
+        const int b0 = warp * 16;
+#pragma unroll
+        for (int i = 0; i < 16; i++) Tm[(b0 + i) * PA_LS + b0 + lane] = 0.f;                      // columns b0 + 16 .. b0 + 31
     }
     __syncthreads();
-    // (2) blocks (1,0) and (3,2): X = -T_bb (L_ba T_aa); 64 threads per pair, 4 outputs each; the product L_ba T_aa is parked in
-    //     the (a, b) block of T, which lies above the diagonal and is never part of the result
+    GDN_TSTAMP(4);
+    // (2) blocks (1,0) and (3,2): T_ba = -T_bb (L_ba T_aa).  Warps 0, 1 take the first pair, warps 2, 3 the second; a warp owns 8 of
+    //     the 16 columns.  The inner product replaces L_ba (nothing reads that block again).
     {
-        const int pair = tid >> 6, u = tid & 63, r = u >> 2, c0 = (u & 3) * 4;
+        const int pair = warp >> 1, n0 = (warp & 1) * 8;
         const int ra = pair * 32, rb = ra + 16;                       // first row of blocks a and b
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int k = 0; k < 16; k++) {
-            const float l = Lm[(rb + r) * PA_LS + ra + k];
-            const float4 t4 = *reinterpret_cast<const float4*>(Tm + (ra + k) * PA_LS + ra + c0);
-            acc[0] += l * t4.x; acc[1] += l * t4.y; acc[2] += l * t4.z; acc[3] += l * t4.w;
-        }
-        *reinterpret_cast<float4*>(Tm + (ra + r) * PA_LS + rb + c0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        const int g = lane >> 2, t = lane & 3;
+        float acc[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+        warp_mm_tf32x3<2, 1>(Lm + rb * PA_LS + ra, PA_LS, Tm + ra * PA_LS + ra + n0, PA_LS, lane, acc);
+        __syncthreads();                                              // every warp has read its operand rows of L_ba
+        *reinterpret_cast<float2*>(Lm + (rb + g) * PA_LS + ra + n0 + 2 * t) = make_float2(acc[0][0], acc[0][1]);
+        *reinterpret_cast<float2*>(Lm + (rb + g + 8) * PA_LS + ra + n0 + 2 * t) = make_float2(acc[0][2], acc[0][3]);
         __syncthreads();
-        float x[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int k = 0; k < 16; k++) {
-            const float tk = Tm[(rb + r) * PA_LS + rb + k];           // T_bb (step (1) wrote the whole block, zeros above the diagonal included)
-            const float4 m4 = *reinterpret_cast<const float4*>(Tm + (ra + k) * PA_LS + rb + c0);
-            x[0] -= tk * m4.x; x[1] -= tk * m4.y; x[2] -= tk * m4.z; x[3] -= tk * m4.w;
-        }
-        *reinterpret_cast<float4*>(Tm + (rb + r) * PA_LS + ra + c0) = make_float4(x[0], x[1], x[2], x[3]);
+        float x[1][4] = {{0.f, 0.f, 0.f, 0.f}};
+        warp_mm_tf32x3<2, 1>(Tm + rb * PA_LS + rb, PA_LS, Lm + rb * PA_LS + ra + n0, PA_LS, lane, x);      // T_bb has zeros above its diagonal
+        *reinterpret_cast<float2*>(Tm + (rb + g) * PA_LS + ra + n0 + 2 * t) = make_float2(-x[0][0], -x[0][1]);
+        *reinterpret_cast<float2*>(Tm + (rb + g + 8) * PA_LS + ra + n0 + 2 * t) = make_float2(-x[0][2], -x[0][3]);
     }
     __syncthreads();
-    // (3) the 32 x 32 block (rows 32..63, columns 0..31): X = -T_hi (L_lo T_lo), T_lo / T_hi = the 32 x 32 diagonal blocks just
-    //     completed; 128 threads, 8 outputs each; the inner product is parked in rows 0..31, columns 32..63 of T
+    GDN_TSTAMP(5);
+    // (3) the 32 x 32 block (rows 32..63, columns 0..31): T_ba = -T_hi (L_ba T_lo), T_lo / T_hi = the 32 x 32 diagonal blocks just
+    //     completed; a warp owns a 16 x 16 quadrant of the result
     {
-        const int r = tid >> 2, c0 = (tid & 3) * 8;
-        float acc[8];
+        const int r0 = (warp & 1) * 16, n0 = (warp >> 1) * 16;
+        const int g = lane >> 2, t = lane & 3;
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        warp_mm_tf32x3<4, 2>(Lm + (32 + r0) * PA_LS, PA_LS, Tm + n0, PA_LS, lane, acc);
+        __syncthreads();                                              // every warp has read its operand rows of L_ba
 #pragma unroll
-        for (int i = 0; i < 8; i++) acc[i] = 0.f;
-#pragma unroll 8
-        for (int k = 0; k < 32; k++) {
-            const float l = Lm[(32 + r) * PA_LS + k];
-            const float4 t0 = *reinterpret_cast<const float4*>(Tm + k * PA_LS + c0);
-            const float4 t1 = *reinterpret_cast<const float4*>(Tm + k * PA_LS + c0 + 4);
-            // T_lo is lower triangular; the entries of its (0,1) block hold the parked product of step (2) and must read as zero
-            const bool up = k < 16;
-            const float m0 = (up && c0 >= 16) ? 0.f : 1.f;
-            acc[0] += l * t0.x * m0; acc[1] += l * t0.y * m0; acc[2] += l * t0.z * m0; acc[3] += l * t0.w * m0;
-            acc[4] += l * t1.x * m0; acc[5] += l * t1.y * m0; acc[6] += l * t1.z * m0; acc[7] += l * t1.w * m0;
+        for (int nt = 0; nt < 2; nt++) {
+            *reinterpret_cast<float2*>(Lm + (32 + r0 + g) * PA_LS + n0 + 8 * nt + 2 * t) = make_float2(acc[nt][0], acc[nt][1]);
+            *reinterpret_cast<float2*>(Lm + (32 + r0 + g + 8) * PA_LS + n0 + 8 * nt + 2 * t) = make_float2(acc[nt][2], acc[nt][3]);
         }
-        *reinterpret_cast<float4*>(Tm + r * PA_LS + 32 + c0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        *reinterpret_cast<float4*>(Tm + r * PA_LS + 32 + c0 + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
         __syncthreads();
-        float x[8];
+        float x[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        warp_mm_tf32x3<4, 2>(Tm + (32 + r0) * PA_LS + 32, PA_LS, Lm + 32 * PA_LS + n0, PA_LS, lane, x);     // T_hi has zeros above its diagonal
 #pragma unroll
-        for (int i = 0; i < 8; i++) x[i] = 0.f;
-#pragma unroll 8
-        for (int k = 0; k < 32; k++) {
-            // T_hi is lower triangular; its (2,3) block (rows 32..47, columns 48..63) holds the parked product of step (2): k <= r excludes it
-            const float tk = k <= r ? Tm[(32 + r) * PA_LS + 32 + k] : 0.f;
-            const float4 m0 = *reinterpret_cast<const float4*>(Tm + k * PA_LS + 32 + c0);
-            const float4 m1 = *reinterpret_cast<const float4*>(Tm + k * PA_LS + 32 + c0 + 4);
-            x[0] -= tk * m0.x; x[1] -= tk * m0.y; x[2] -= tk * m0.z; x[3] -= tk * m0.w;
-            x[4] -= tk * m1.x; x[5] -= tk * m1.y; x[6] -= tk * m1.z; x[7] -= tk * m1.w;
+        for (int nt = 0; nt < 2; nt++) {
+            *reinterpret_cast<float2*>(Tm + (32 + r0 + g) * PA_LS + n0 + 8 * nt + 2 * t) = make_float2(-x[nt][0], -x[nt][1]);
+            *reinterpret_cast<float2*>(Tm + (32 + r0 + g + 8) * PA_LS + n0 + 8 * nt + 2 * t) = make_float2(-x[nt][2], -x[nt][3]);
         }
-        *reinterpret_cast<float4*>(Tm + (32 + r) * PA_LS + c0) = make_float4(x[0], x[1], x[2], x[3]);
-        *reinterpret_cast<float4*>(Tm + (32 + r) * PA_LS + c0 + 4) = make_float4(x[4], x[5], x[6], x[7]);
     }
     __syncthreads();
 
+    GDN_TSTAMP(6);
     // ---- record: Tb = T diag(beta) as bf16 hi / lo operand images, then the gate vectors ----
     unsigned char* rec = a.records + ((size_t)slot * a.H + h) * PA_REC_BYTES;
     {
         const int i = tid >> 1, hf = tid & 1;
 #pragma unroll
         for (int cb = 0; cb < 4; cb++) {
-            uint32_t bh[4], bl[4];
+            uint32_t bh[4] = {0u, 0u, 0u, 0u}, bl[4] = {0u, 0u, 0u, 0u};
+            if (hf * 32 + cb * 8 <= i)                                // pieces entirely above the diagonal are zero: nothing to read or split
 #pragma unroll
             for (int e = 0; e < 4; e += 2) {
                 const int j = hf * 32 + cb * 8 + 2 * e;
@@ -352,6 +410,7 @@ gdn_phase_a_kernel(const __grid_constant__ CUtensorMap tmK, const PhaseAArgs a) 
     }
     tc_fence_before_sync();
     __syncthreads();
+    GDN_TSTAMP(7);
     if (warp == 0) tmem_dealloc(tb, 64);
 }
 
@@ -389,3 +448,9 @@ int launch_phase_a(const void* k, const PhaseAArgs& a, bool fused, cudaStream_t 
 }
 
 }  // namespace gdn
+
+#ifdef GDN_TIMING
+extern "C" int gdn_timing_log_a(long long* out_host, int n) {
+    return cudaMemcpyFromSymbol(out_host, gdn::g_tlog, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
+}
+#endif

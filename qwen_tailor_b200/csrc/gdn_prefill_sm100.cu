@@ -196,6 +196,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             // ---- Z = -P1^T diag(gamma) -> bf16 hi/lo pairs in TMEM (the A operand of Z Tb^T) ----
             if (!wait(B_P1DONE, par)) break;
             tc_fence_after_sync();
+            if (warp == 0) GDN_TSTAMP(64 + c * 16 + 8);
             {
                 const float* gam = stage_f(c, ST_GAM);
                 uint32_t rr[32], hi[16], lo[16];
@@ -213,10 +214,12 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             tc_fence_before_sync();
             warp_arrive(B_ZREADY);
+            if (warp == 0) GDN_TSTAMP(64 + c * 16 + 9);
 
             // ---- D^T -> bf16 hi/lo pairs in TMEM (A operand of D^T A^T) and Dp^T = D^T diag(dec) -> hi/lo K-major rows in smem ----
             if (!wait(B_DDONE, par)) break;
             tc_fence_after_sync();
+            if (warp == 0) GDN_TSTAMP(64 + c * 16 + 10);
             {
                 const float* dec = stage_f(c, ST_DEC);
                 uint32_t rr[32], hi[16], lo[16];
@@ -245,6 +248,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             fence_proxy_async_smem();
             tc_fence_before_sync();
             warp_arrive(B_DPREADY);
+            if (warp == 0) GDN_TSTAMP(64 + c * 16 + 11);
             warp_arrive((c & 1) ? B_EMPTY1 : B_EMPTY0);              // this warp's last read of the stage (gamma, dec) is behind it
 
             // ---- after the state update: bf16 hi/lo pairs of the new state for the next chunk's products, fp32 copy pre-scaled by
@@ -256,6 +260,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             if (!wait(B_SDONE, par)) break;
             tc_fence_after_sync();
+            if (warp == 0) GDN_TSTAMP(64 + c * 16 + 12);
 #pragma unroll
             for (int blk = 0; blk < 2; blk++) {
                 uint32_t rr[32], hi[16], lo[16];
@@ -281,6 +286,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 tmem_wait_st();
                 tc_fence_before_sync();
                 warp_arrive(B_SREADY);
+                if (warp == 0) GDN_TSTAMP(64 + c * 16 + 13);
             }
         }
     } else if (warp < N_CHAIN_WARPS + N_OUT_WARPS) {
@@ -335,6 +341,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             // ---- y[t0 + i, h, v] = gamma_i P2^T[v][i] + YD^T[v][i]: each lane owns one value row, a warp store covers 64 contiguous bytes ----
             if (!wait(B_YDONE, par)) break;
             tc_fence_after_sync();
+            if (warp == 8) GDN_TSTAMP(64 + c * 16 + 14);
             {
                 __nv_bfloat16* yp = a.y + ((size_t)t0 * a.H + h) * DV + r;
                 const float* gam = stage_f(c, ST_GAM);
@@ -374,6 +381,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 for (int ii = 0; ii < 32; ii++)
                     if (32 + ii < nrows) yp[(size_t)(32 + ii) * a.H * DV] = __float2bfloat16_rn(__uint_as_float(yb[ii]));
             }
+            if (warp == 8) GDN_TSTAMP(64 + c * 16 + 15);
         }
     } else if (warp == 12) {
         // ============================================================================================================
@@ -391,6 +399,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 // ---- P1^T = S0 K^T (S0 = hi + lo from TMEM) ----
                 if (!wait_full(c) || !wait(B_SREADY, par)) break;
                 tc_fence_after_sync();
+                GDN_TSTAMP(64 + c * 16 + 0);
 #pragma unroll
                 for (int part = 0; part < 2; part++) {
                     const uint32_t acol = part ? TM_SLO : TM_SHI;
@@ -401,6 +410,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     }
                 }
                 mma_commit(bar(B_P1DONE));
+                GDN_TSTAMP(64 + c * 16 + 1);
                 // ---- state-independent products while the chain warps convert P1: G = [K; Q] K^T and V^T Tb^T (the start of D^T).
                 //      Their accumulators held the previous chunk's YD^T and P2^T until the output warps had read them ----
                 if (c >= 1 && !wait(B_YFREE, par - 1)) break;
@@ -423,6 +433,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 // ---- D^T += Z Tb^T ----
                 if (!wait(B_ZREADY, par)) break;
                 tc_fence_after_sync();
+                GDN_TSTAMP(64 + c * 16 + 2);
 #pragma unroll
                 for (int term = 0; term < 3; term++) {
                     const uint32_t acol = term == 1 ? TM_ZLO : TM_ZHI;
@@ -431,6 +442,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     for (int ks = 0; ks < 4; ks++) mma_ts(tb + tm_d, tb + acol + ks * 8, smem_desc_sw128(bsm + ks * 32, 16, 1024), I64, 1);
                 }
                 mma_commit(bar(B_DDONE));
+                GDN_TSTAMP(64 + c * 16 + 3);
                 // ---- P2^T = S0 Q^T into the columns P1 has left; it runs while the chain warps convert D ----
 #pragma unroll
                 for (int part = 0; part < 2; part++) {
@@ -444,6 +456,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 // ---- the state update S += Dp^T K ----
                 if (!wait(B_DPREADY, par)) break;
                 tc_fence_after_sync();
+                GDN_TSTAMP(64 + c * 16 + 4);
 #pragma unroll
                 for (int part = 0; part < 2; part++) {
                     const uint32_t asm_ = sbase + (part ? SM_DP_LO : SM_DP_HI);
@@ -452,9 +465,11 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                         mma_ss(tb + TM_S, smem_desc_sw128(asm_ + ks * 32, 16, 1024), smem_desc_sw128(st + ST_K0 + ks * 2048, 16384, 1024), I128_BMN, 1);
                 }
                 mma_commit(bar(B_SDONE));
+                GDN_TSTAMP(64 + c * 16 + 5);
                 // ---- YD^T = D^T A^T over the columns G has left ----
                 if (!wait(B_AREADY, par)) break;
                 tc_fence_after_sync();
+                GDN_TSTAMP(64 + c * 16 + 6);
 #pragma unroll
                 for (int term = 0; term < 3; term++) {
                     const uint32_t acol = term == 1 ? TM_ZLO : TM_ZHI;
@@ -463,6 +478,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     for (int ks = 0; ks < 4; ks++) mma_ts(tb + TM_GY, tb + acol + ks * 8, smem_desc_sw128(bsm + ks * 32, 16, 1024), I64, (term | ks) != 0);
                 }
                 mma_commit(bar(B_YDONE));
+                GDN_TSTAMP(64 + c * 16 + 7);
                 mma_commit(bar((c & 1) ? B_EMPTY1 : B_EMPTY0));      // every MMA that reads this stage has completed when this arrives
             }
         }
@@ -569,3 +585,9 @@ int launch_phase_b(const void* q, const void* k, const void* v, const PrefillArg
 }
 
 }  // namespace gdn
+
+#ifdef GDN_TIMING
+extern "C" int gdn_timing_log_b(long long* out_host, int n) {
+    return cudaMemcpyFromSymbol(out_host, gdn::g_tlog, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
+}
+#endif
