@@ -14,20 +14,22 @@
 // Mapping.  One block = one (sequence, head) chain; the chain over chunks is serial, heads / sequences / layers are the parallel
 // axis.  Every product is computed TRANSPOSED so that the 128 value rows of the head are the M dimension of a full-rate M = 128
 // MMA and a TMEM lane is one value row for the whole kernel:
-//     P1^T [dv x 64]   = S0 K^T,  P2^T = S0 Q^T                         A = S0 (bf16 hi + lo) from TMEM
-//     G    [128 x 64]  = [K; Q] K^T            rows 64-127 = Q K^T (K and Q tiles are stacked in smem); rows 0-63 are not used
-//     D^T  [dv x 64]   = V^T Tb^T + Z Tb^T,  Z = -P1^T diag(gamma)      A = V read MN-major from smem / Z (hi + lo) from TMEM
+//     [P1^T | P2^T] [dv x 128] = S0 [K; Q]^T                            A = S0 (bf16 hi + lo) from TMEM; K and Q tiles are stacked in
+//                                                                       smem, so one N = 128 product gives S0 K^T and S0 Q^T
+//     G    [128 x 64]  = [K; Q] K^T            rows 64-127 = Q K^T; rows 0-63 are not used
+//     D^T  [dv x 64]   = R^T Tb^T,  R^T = V^T - P1^T diag(gamma)        A = R^T (hi + lo) from TMEM (the chain warps form it in fp32)
 //     YD^T [dv x 64]   = D^T A^T                                        A = D^T (hi + lo) from TMEM, B = A (hi + lo) in smem
 //     S    [dv x 128] += Dp^T K,  Dp = diag(dec) D                      A = Dp^T (hi + lo) in smem, B = K read MN-major
-// The fp32 state lives in TMEM for the whole sequence.  Every operand that is derived from fp32 data (S, Z, D, Dp, Tb, A) is fed to
+// The fp32 state lives in TMEM for the whole sequence.  Every operand that is derived from fp32 data (S, R, D, Dp, Tb, A) is fed to
 // the bf16 MMA as an exact hi + lo pair (16 significand bits), which keeps the final state within 1e-4 of fp64; K, Q and V are
 // bf16 already.
 //
 // Roles (448 threads, one block per SM):
 //   warps 0-7   "chain": the state-dependent passes between MMAs (two warps per TMEM lane quadrant, half of the columns each)
 //   warps 8-11  "output": the A matrix from Q K^T, and y = gamma * P2 + YD
-//   warp 12     lane 0 issues every tcgen05.mma, ordered so that the tensor pipe works on state-independent products (G, V^T Tb^T,
-//               P2, YD) while the chain warps convert the state-dependent ones
+//   warp 12     lane 0 issues every tcgen05.mma.  An MMA instruction of this shape occupies the tensor pipe for ~90 cycles whatever
+//               its N <= 128 (measured), so the kernel is bound by the NUMBER of instructions per chunk: 56 (16 for [P1 | P2],
+//               8 for G, 12 for D, 8 for the state update, 12 for YD); G and YD run while the chain warps convert
 //   warp 13     "producer": K / Q / V tiles by TMA (128-byte swizzle, no multicast) and the phase-A record by one bulk copy, two
 //               stages; it also zeroes the rows of a partial last chunk so that a packed neighbour sequence can never leak in
 // The groups hand over through mbarriers.  Two rules keep that protocol sound: every warp that waits on a barrier also takes part
@@ -58,20 +60,21 @@ constexpr int SM_A_HI = 2 * SM_STAGE;                // A as bf16 hi / lo: [64][
 constexpr int SM_A_LO = SM_A_HI + 8192;
 constexpr int SM_DP_HI = SM_A_LO + 8192;             // Dp^T hi / lo: [128][64] bf16, K-major, 16 KiB each
 constexpr int SM_DP_LO = SM_DP_HI + 16384;
-constexpr int SM_TOTAL = SM_DP_LO + 16384;
+constexpr int SM_Y = SM_DP_LO + 16384;               // y tile of the chunk, [64 tokens][128 value columns] bf16, staged for row-wise stores (16 KiB)
+constexpr int SM_TOTAL = SM_Y + 16384;
 static_assert(ST_DEC + 256 <= SM_STAGE && ST_DEC + 256 - ST_REC == PA_REC_BYTES, "record layout");
 // ---- tensor memory map (columns) ----
 constexpr uint32_t TM_S = 0;                         // fp32 state, pre-scaled by the coming chunk's gamma_C   [128 cols]
 constexpr uint32_t TM_SHI = 128, TM_SLO = 192;       // bf16 pairs of the unscaled state                        [64 + 64]
-constexpr uint32_t TM_GY = 256;                      // [K;Q] K^T, later YD^T                                   [64]
-constexpr uint32_t TM_RA = 320, TM_RB = 384;         // chunk parity picks which holds P1^T / P2^T and which D^T [64 + 64]
-constexpr uint32_t TM_ZHI = 448, TM_ZLO = 480;       // Z, later D^T, as bf16 pairs                             [32 + 32]
+constexpr uint32_t TM_X = 256;                       // [P1^T | P2^T]; once P1 has been consumed its half takes D^T  [64 + 64]
+constexpr uint32_t TM_GY = 384;                      // [K;Q] K^T, later YD^T                                   [64]
+constexpr uint32_t TM_ZHI = 448, TM_ZLO = 480;       // R^T, later D^T, as bf16 pairs                           [32 + 32]
 // ---- mbarriers ----
 enum { B_RAW0 = 0, B_RAW1, B_FULL0, B_FULL1, B_EMPTY0, B_EMPTY1, B_SREADY, B_P1DONE, B_ZREADY, B_DDONE, B_DPREADY, B_SDONE, B_GDONE, B_AREADY,
        B_YDONE, B_YFREE, B_COUNT };
 constexpr int N_CHAIN_WARPS = 8, N_OUT_WARPS = 4;
 
-constexpr uint32_t WAIT_LIMIT = 400000u;
+constexpr uint32_t WAIT_LIMIT = 2000000u;               // polls of >= 20 ns each: tens of milliseconds before a wait gives up
 
 __device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 
@@ -94,6 +97,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     __shared__ uint64_t bars[B_COUNT];
     __shared__ uint32_t tmem_slot;
     __shared__ int s_abort;
+    __shared__ int s_group_ok[2];                                    // verdict of the chain / output group's polling warp on its last wait
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.x / a.n_heads, h = a.head_lo + blockIdx.x % a.n_heads;
@@ -126,7 +130,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_init(bar(B_SREADY), N_CHAIN_WARPS); mbar_init(bar(B_ZREADY), N_CHAIN_WARPS); mbar_init(bar(B_DPREADY), N_CHAIN_WARPS);
         mbar_init(bar(B_AREADY), N_OUT_WARPS); mbar_init(bar(B_YFREE), N_OUT_WARPS);
         mbar_init(bar(B_P1DONE), 1); mbar_init(bar(B_DDONE), 1); mbar_init(bar(B_SDONE), 1); mbar_init(bar(B_GDONE), 1); mbar_init(bar(B_YDONE), 1);
-        s_abort = 0;
+        s_abort = 0; s_group_ok[0] = 1; s_group_ok[1] = 1;
         fence_barrier_init();
         tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
     }
@@ -144,9 +148,11 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     auto aborted = [&]() -> bool { return *(volatile int*)&s_abort != 0; };
     // a bounded wait; on failure (or when another warp has already given up) the whole block is told to leave
     auto wait = [&](int b, uint32_t parity) -> bool {
+        // non-blocking polls with a short pause in between: the suspending form of the wait (try_wait) costs ~250 cycles per call on
+        // this part even when the phase has long completed, which the issuing thread would pay six times per chunk
         const uint32_t addr = bar(b);
         for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-            if (mbar_try_wait(addr, parity & 1u)) return true;
+            if (mbar_test_wait(addr, parity & 1u)) return true;
             if ((i & 63u) == 63u && aborted()) return false;
             __nanosleep(GDN_POLL_SLEEP);
         }
@@ -155,6 +161,21 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         return false;
     };
     auto wait_full = [&](int c) -> bool { return wait((c & 1) ? B_FULL1 : B_FULL0, (uint32_t)(c >> 1)); };
+    // Waits of a warp group.  One warp polls the mbarrier and the others block on a hardware barrier: a polling warp takes issue
+    // slots on its scheduler, and the scheduler of the MMA-issuing warp must stay free of pollers (measured: with all fourteen
+    // warps polling, every wait of the issuing thread cost ~300 cycles even when its barrier had long completed).  The polling
+    // warp's verdict is published before the group barrier, so the whole group takes the same exit -- a warp that left on its
+    // own would strand the others at a barrier that has no timeout.
+    auto chain_wait = [&](int b, uint32_t parity) -> bool {        // warps 0-7; warp 1 polls (warp 12 issues MMAs on scheduler 0)
+        if (warp == 1) { const bool okw = wait(b, parity); if (lane == 0) s_group_ok[0] = okw ? 1 : 0; }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        return *(volatile int*)&s_group_ok[0] != 0;
+    };
+    auto out_wait = [&](int b, uint32_t parity) -> bool {          // warps 8-11; warp 10 polls
+        if (warp == 10) { const bool okw = wait(b, parity); if (lane == 0) s_group_ok[1] = okw ? 1 : 0; }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        return *(volatile int*)&s_group_ok[1] != 0;
+    };
 
     if (warp < N_CHAIN_WARPS) {
         // ============================================================================================================
@@ -163,7 +184,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int q = warp & 3, hf = warp >> 2;
         const int r = q * 32 + lane;                                 // value row of this thread
         const uint32_t tl = tb + ((uint32_t)(q * 32) << 16);
-        bool ok = wait_full(0);
+        bool ok = chain_wait(B_FULL0, 0);
         // ---- initial state -> TMEM: unscaled bf16 hi/lo pairs and the fp32 copy pre-scaled by gamma_C of chunk 0 ----
         if (ok) {
             const float gC0 = stage_f(0, ST_GAM)[63];
@@ -190,23 +211,32 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int c = 0; ok && c < nchunks; c++) {
             const uint32_t par = (uint32_t)c;
             const bool last = c == nchunks - 1;
-            const uint32_t tm_x = (c & 1) ? TM_RB : TM_RA, tm_d = (c & 1) ? TM_RA : TM_RB;
-            if (aborted()) break;
 
-            // ---- Z = -P1^T diag(gamma) -> bf16 hi/lo pairs in TMEM (the A operand of Z Tb^T) ----
-            if (!wait(B_P1DONE, par)) break;
+            // ---- R^T = V^T - P1^T diag(gamma) -> bf16 hi/lo pairs in TMEM (the A operand of R^T Tb^T) ----
+            if (!chain_wait(B_P1DONE, par)) break;
             tc_fence_after_sync();
-            if (warp == 0) GDN_TSTAMP(64 + c * 16 + 8);
+            if (warp == 0) GDN_TSTAMP(64 + c * 32 + 8);
             {
                 const float* gam = stage_f(c, ST_GAM);
+                // V[j][r] of the chunk's tokens j = 32 hf .. 32 hf + 31: the V tile holds rows of 64 value columns (128 bytes, swizzled
+                // in 16-byte pieces), so the lanes of a warp read 64 contiguous bytes of one row
+                const unsigned char* vt = smem + (c & 1) * SM_STAGE + ST_V + (r >> 6) * 8192 + (r & 7) * 2;
+                const int vp = (r & 63) >> 3;
                 uint32_t rr[32], hi[16], lo[16];
-                tmem_ld32(tl + tm_x + hf * 32, rr);
+                tmem_ld32(tl + TM_X + hf * 32, rr);
+                float vv[32];
+#pragma unroll
+                for (int jj = 0; jj < 32; jj++) {
+                    const int j = hf * 32 + jj;
+                    vv[jj] = __uint_as_float((uint32_t)*reinterpret_cast<const unsigned short*>(vt + j * 128 + ((vp ^ (j & 7)) << 4)) << 16);
+                }
                 tmem_wait_ld();
 #pragma unroll
                 for (int jj = 0; jj < 32; jj += 4) {
                     const float4 g4 = *reinterpret_cast<const float4*>(gam + hf * 32 + jj);
-                    split_pack(-g4.x * __uint_as_float(rr[jj]), -g4.y * __uint_as_float(rr[jj + 1]), hi[jj / 2], lo[jj / 2]);
-                    split_pack(-g4.z * __uint_as_float(rr[jj + 2]), -g4.w * __uint_as_float(rr[jj + 3]), hi[jj / 2 + 1], lo[jj / 2 + 1]);
+                    split_pack(fmaf(-g4.x, __uint_as_float(rr[jj]), vv[jj]), fmaf(-g4.y, __uint_as_float(rr[jj + 1]), vv[jj + 1]), hi[jj / 2], lo[jj / 2]);
+                    split_pack(fmaf(-g4.z, __uint_as_float(rr[jj + 2]), vv[jj + 2]), fmaf(-g4.w, __uint_as_float(rr[jj + 3]), vv[jj + 3]), hi[jj / 2 + 1],
+                               lo[jj / 2 + 1]);
                 }
                 tmem_st16(tl + TM_ZHI + hf * 16, hi);
                 tmem_st16(tl + TM_ZLO + hf * 16, lo);
@@ -214,16 +244,16 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
             tc_fence_before_sync();
             warp_arrive(B_ZREADY);
-            if (warp == 0) GDN_TSTAMP(64 + c * 16 + 9);
+            if (warp == 0) GDN_TSTAMP(64 + c * 32 + 9);
 
             // ---- D^T -> bf16 hi/lo pairs in TMEM (A operand of D^T A^T) and Dp^T = D^T diag(dec) -> hi/lo K-major rows in smem ----
-            if (!wait(B_DDONE, par)) break;
+            if (!chain_wait(B_DDONE, par)) break;
             tc_fence_after_sync();
-            if (warp == 0) GDN_TSTAMP(64 + c * 16 + 10);
+            if (warp == 0) GDN_TSTAMP(64 + c * 32 + 10);
             {
                 const float* dec = stage_f(c, ST_DEC);
                 uint32_t rr[32], hi[16], lo[16];
-                tmem_ld32(tl + tm_d + hf * 32, rr);
+                tmem_ld32(tl + TM_X + hf * 32, rr);
                 tmem_wait_ld();
 #pragma unroll
                 for (int jj = 0; jj < 32; jj += 2) split_pack(__uint_as_float(rr[jj]), __uint_as_float(rr[jj + 1]), hi[jj / 2], lo[jj / 2]);
@@ -248,19 +278,19 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             fence_proxy_async_smem();
             tc_fence_before_sync();
             warp_arrive(B_DPREADY);
-            if (warp == 0) GDN_TSTAMP(64 + c * 16 + 11);
+            if (warp == 0) GDN_TSTAMP(64 + c * 32 + 11);
             warp_arrive((c & 1) ? B_EMPTY1 : B_EMPTY0);              // this warp's last read of the stage (gamma, dec) is behind it
 
             // ---- after the state update: bf16 hi/lo pairs of the new state for the next chunk's products, fp32 copy pre-scaled by
             //      the next chunk's gamma_C (or the final state) ----
             float gC_next = 1.f;
             if (!last) {
-                if (!wait_full(c + 1)) break;
+                if (!chain_wait(((c + 1) & 1) ? B_FULL1 : B_FULL0, (uint32_t)((c + 1) >> 1))) break;
                 gC_next = stage_f(c + 1, ST_GAM)[63];
             }
-            if (!wait(B_SDONE, par)) break;
+            if (!chain_wait(B_SDONE, par)) break;
             tc_fence_after_sync();
-            if (warp == 0) GDN_TSTAMP(64 + c * 16 + 12);
+            if (warp == 0) GDN_TSTAMP(64 + c * 32 + 12);
 #pragma unroll
             for (int blk = 0; blk < 2; blk++) {
                 uint32_t rr[32], hi[16], lo[16];
@@ -286,7 +316,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 tmem_wait_st();
                 tc_fence_before_sync();
                 warp_arrive(B_SREADY);
-                if (warp == 0) GDN_TSTAMP(64 + c * 16 + 13);
+                if (warp == 0) GDN_TSTAMP(64 + c * 32 + 13);
             }
         }
     } else if (warp < N_CHAIN_WARPS + N_OUT_WARPS) {
@@ -298,13 +328,11 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint32_t tl = tb + ((uint32_t)(q * 32) << 16);
         for (int c = 0; c < nchunks; c++) {
             const uint32_t par = (uint32_t)c;
-            const uint32_t tm_x = (c & 1) ? TM_RB : TM_RA;
             const int t0 = t_begin + c * CH;
             const int nrows = min(CH, t_end - t0);
-            if (aborted()) break;
-            if (!wait_full(c)) break;                                // Lc and gamma of the chunk are visible to this warp
+            if (!out_wait((c & 1) ? B_FULL1 : B_FULL0, (uint32_t)(c >> 1))) break;      // Lc and gamma of the chunk have landed
             // ---- A = lower_incl(exp(Lc_i - Lc_j) Q K^T) as bf16 hi/lo K-major rows (the previous chunk's D^T A^T has completed) ----
-            if (!wait(B_GDONE, par)) break;
+            if (!out_wait(B_GDONE, par)) break;
             tc_fence_after_sync();
             if (q >= 2) {
                 const int i = r - 64;
@@ -339,16 +367,15 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             tc_fence_before_sync();
             warp_arrive(B_AREADY);                                   // all four warps: each of them waited on B_GDONE (see the rule above)
             // ---- y[t0 + i, h, v] = gamma_i P2^T[v][i] + YD^T[v][i]: each lane owns one value row, a warp store covers 64 contiguous bytes ----
-            if (!wait(B_YDONE, par)) break;
+            if (!out_wait(B_YDONE, par)) break;
             tc_fence_after_sync();
-            if (warp == 8) GDN_TSTAMP(64 + c * 16 + 14);
+            if (warp == 8) GDN_TSTAMP(64 + c * 32 + 14);
             {
-                __nv_bfloat16* yp = a.y + ((size_t)t0 * a.H + h) * DV + r;
                 const float* gam = stage_f(c, ST_GAM);
                 uint32_t ya[32], yb[32];
                 {
                     uint32_t yd[32];
-                    tmem_ld32(tl + tm_x, ya);
+                    tmem_ld32(tl + TM_X + 64, ya);
                     tmem_ld32(tl + TM_GY, yd);
                     tmem_wait_ld();
 #pragma unroll
@@ -359,7 +386,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                         ya[ii + 2] = __float_as_uint(fmaf(g4.z, __uint_as_float(ya[ii + 2]), __uint_as_float(yd[ii + 2])));
                         ya[ii + 3] = __float_as_uint(fmaf(g4.w, __uint_as_float(ya[ii + 3]), __uint_as_float(yd[ii + 3])));
                     }
-                    tmem_ld32(tl + tm_x + 32, yb);
+                    tmem_ld32(tl + TM_X + 96, yb);
                     tmem_ld32(tl + TM_GY + 32, yd);
                     tmem_wait_ld();
                     tc_fence_before_sync();
@@ -374,14 +401,29 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     }
                 }
                 warp_arrive((c & 1) ? B_EMPTY1 : B_EMPTY0);          // gamma was this warp's last read of the stage
+                // transpose through shared memory: a lane owns one value column of all 64 tokens, the rows of y want 256 contiguous bytes
+                __nv_bfloat16* ys = reinterpret_cast<__nv_bfloat16*>(smem + SM_Y);
+                unsigned short* ysu = reinterpret_cast<unsigned short*>(ys);
 #pragma unroll
-                for (int ii = 0; ii < 32; ii++)
-                    if (ii < nrows) yp[(size_t)ii * a.H * DV] = __float2bfloat16_rn(__uint_as_float(ya[ii]));
+                for (int ii = 0; ii < 32; ii += 2) {                 // packed conversions (two tokens at a time), 16-bit stores
+                    const uint32_t pa = pack_bf16x2(__uint_as_float(ya[ii]), __uint_as_float(ya[ii + 1]));
+                    const uint32_t pb = pack_bf16x2(__uint_as_float(yb[ii]), __uint_as_float(yb[ii + 1]));
+                    ysu[ii * DV + r] = (unsigned short)pa;
+                    ysu[(ii + 1) * DV + r] = (unsigned short)(pa >> 16);
+                    ysu[(32 + ii) * DV + r] = (unsigned short)pb;
+                    ysu[(33 + ii) * DV + r] = (unsigned short)(pb >> 16);
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");       // the four output warps
+                const int ot = tid - N_CHAIN_WARPS * 32;             // 0..127
 #pragma unroll
-                for (int ii = 0; ii < 32; ii++)
-                    if (32 + ii < nrows) yp[(size_t)(32 + ii) * a.H * DV] = __float2bfloat16_rn(__uint_as_float(yb[ii]));
+                for (int k = 0; k < 8; k++) {
+                    const int p = ot + 128 * k, i = p >> 4, c16 = p & 15;
+                    if (i < nrows)
+                        *reinterpret_cast<uint4*>(a.y + ((size_t)(t0 + i) * a.H + h) * DV + c16 * 8) = *reinterpret_cast<const uint4*>(ys + i * DV + c16 * 8);
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");       // the tile may be overwritten by the next chunk
             }
-            if (warp == 8) GDN_TSTAMP(64 + c * 16 + 15);
+            if (warp == 8) GDN_TSTAMP(64 + c * 32 + 15);
         }
     } else if (warp == 12) {
         // ============================================================================================================
@@ -389,32 +431,33 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         // ============================================================================================================
         if (lane == 0) {
             constexpr uint32_t I64 = idesc_bf16(128, 64, 0, 0);      // N = 64, A and B K-major (A may also come from TMEM)
-            constexpr uint32_t I64_AMN = idesc_bf16(128, 64, 1, 0);  // N = 64, A read MN-major (V as V^T)
+            constexpr uint32_t I128 = idesc_bf16(128, 128, 0, 0);    // N = 128: B = the stacked [K; Q] rows
             constexpr uint32_t I128_BMN = idesc_bf16(128, 128, 0, 1);// N = 128, B read MN-major (K as the [tokens x dk] factor)
             for (int c = 0; c < nchunks; c++) {
                 const uint32_t par = (uint32_t)c;
                 const uint32_t st = sbase + (c & 1) * SM_STAGE;
-                const uint32_t tm_x = (c & 1) ? TM_RB : TM_RA, tm_d = (c & 1) ? TM_RA : TM_RB;
                 if (aborted()) break;
-                // ---- P1^T = S0 K^T (S0 = hi + lo from TMEM) ----
-                if (!wait_full(c) || !wait(B_SREADY, par)) break;
+                // ---- [P1^T | P2^T] = S0 [K; Q]^T (S0 = hi + lo from TMEM).  The accumulator columns held the previous chunk's P2^T and
+                //      D^T; the G / YD columns its YD^T: both are free once the output warps have read that chunk's y ----
+                if (!wait_full(c)) break;
+                GDN_TSTAMP(64 + c * 32 + 16);
+                if (!wait(B_SREADY, par)) break;
+                GDN_TSTAMP(64 + c * 32 + 17);
+                if (c >= 1 && !wait(B_YFREE, par - 1)) break;
                 tc_fence_after_sync();
-                GDN_TSTAMP(64 + c * 16 + 0);
+                GDN_TSTAMP(64 + c * 32 + 0);
 #pragma unroll
                 for (int part = 0; part < 2; part++) {
                     const uint32_t acol = part ? TM_SLO : TM_SHI;
 #pragma unroll
                     for (int ks = 0; ks < 8; ks++) {
                         const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-                        mma_ts(tb + tm_x, tb + acol + ks * 8, smem_desc_sw128(st + ST_K0 + off, 16, 1024), I64, (part | ks) != 0);
+                        mma_ts(tb + TM_X, tb + acol + ks * 8, smem_desc_sw128(st + ST_K0 + off, 16, 1024), I128, (part | ks) != 0);
                     }
                 }
                 mma_commit(bar(B_P1DONE));
-                GDN_TSTAMP(64 + c * 16 + 1);
-                // ---- state-independent products while the chain warps convert P1: G = [K; Q] K^T and V^T Tb^T (the start of D^T).
-                //      Their accumulators held the previous chunk's YD^T and P2^T until the output warps had read them ----
-                if (c >= 1 && !wait(B_YFREE, par - 1)) break;
-                tc_fence_after_sync();
+                GDN_TSTAMP(64 + c * 32 + 1);
+                // ---- G = [K; Q] K^T: state-independent, runs while the chain warps form R ----
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {
                     const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
@@ -422,41 +465,24 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     mma_ss(tb + TM_GY, d, d, I64, ks > 0);
                 }
                 mma_commit(bar(B_GDONE));
-#pragma unroll
-                for (int part = 0; part < 2; part++) {
-                    const uint32_t bsm = st + (part ? ST_TB_LO : ST_TB_HI);
-#pragma unroll
-                    for (int ks = 0; ks < 4; ks++)
-                        mma_ss(tb + tm_d, smem_desc_sw128(st + ST_V + ks * 2048, 8192, 1024), smem_desc_sw128(bsm + ks * 32, 16, 1024), I64_AMN,
-                               (part | ks) != 0);
-                }
-                // ---- D^T += Z Tb^T ----
+                // ---- D^T = R^T Tb^T over the columns P1 has left ----
                 if (!wait(B_ZREADY, par)) break;
                 tc_fence_after_sync();
-                GDN_TSTAMP(64 + c * 16 + 2);
+                GDN_TSTAMP(64 + c * 32 + 2);
 #pragma unroll
                 for (int term = 0; term < 3; term++) {
                     const uint32_t acol = term == 1 ? TM_ZLO : TM_ZHI;
                     const uint32_t bsm = st + (term == 2 ? ST_TB_LO : ST_TB_HI);
 #pragma unroll
-                    for (int ks = 0; ks < 4; ks++) mma_ts(tb + tm_d, tb + acol + ks * 8, smem_desc_sw128(bsm + ks * 32, 16, 1024), I64, 1);
+                    for (int ks = 0; ks < 4; ks++)
+                        mma_ts(tb + TM_X, tb + acol + ks * 8, smem_desc_sw128(bsm + ks * 32, 16, 1024), I64, (term | ks) != 0);
                 }
                 mma_commit(bar(B_DDONE));
-                GDN_TSTAMP(64 + c * 16 + 3);
-                // ---- P2^T = S0 Q^T into the columns P1 has left; it runs while the chain warps convert D ----
-#pragma unroll
-                for (int part = 0; part < 2; part++) {
-                    const uint32_t acol = part ? TM_SLO : TM_SHI;
-#pragma unroll
-                    for (int ks = 0; ks < 8; ks++) {
-                        const uint32_t off = (ks >> 2) * 16384 + (ks & 3) * 32;
-                        mma_ts(tb + tm_x, tb + acol + ks * 8, smem_desc_sw128(st + ST_Q0 + off, 16, 1024), I64, (part | ks) != 0);
-                    }
-                }
+                GDN_TSTAMP(64 + c * 32 + 3);
                 // ---- the state update S += Dp^T K ----
                 if (!wait(B_DPREADY, par)) break;
                 tc_fence_after_sync();
-                GDN_TSTAMP(64 + c * 16 + 4);
+                GDN_TSTAMP(64 + c * 32 + 4);
 #pragma unroll
                 for (int part = 0; part < 2; part++) {
                     const uint32_t asm_ = sbase + (part ? SM_DP_LO : SM_DP_HI);
@@ -465,11 +491,11 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                         mma_ss(tb + TM_S, smem_desc_sw128(asm_ + ks * 32, 16, 1024), smem_desc_sw128(st + ST_K0 + ks * 2048, 16384, 1024), I128_BMN, 1);
                 }
                 mma_commit(bar(B_SDONE));
-                GDN_TSTAMP(64 + c * 16 + 5);
+                GDN_TSTAMP(64 + c * 32 + 5);
                 // ---- YD^T = D^T A^T over the columns G has left ----
                 if (!wait(B_AREADY, par)) break;
                 tc_fence_after_sync();
-                GDN_TSTAMP(64 + c * 16 + 6);
+                GDN_TSTAMP(64 + c * 32 + 6);
 #pragma unroll
                 for (int term = 0; term < 3; term++) {
                     const uint32_t acol = term == 1 ? TM_ZLO : TM_ZHI;
@@ -478,7 +504,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     for (int ks = 0; ks < 4; ks++) mma_ts(tb + TM_GY, tb + acol + ks * 8, smem_desc_sw128(bsm + ks * 32, 16, 1024), I64, (term | ks) != 0);
                 }
                 mma_commit(bar(B_YDONE));
-                GDN_TSTAMP(64 + c * 16 + 7);
+                GDN_TSTAMP(64 + c * 32 + 7);
                 mma_commit(bar((c & 1) ? B_EMPTY1 : B_EMPTY0));      // every MMA that reads this stage has completed when this arrives
             }
         }

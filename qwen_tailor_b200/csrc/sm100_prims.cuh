@@ -29,6 +29,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uin
                  : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
     return ok != 0;
 }
+// Non-blocking poll: returns at once whether the phase has completed.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after `limit` polls and returns false.  The caller records the failure and leaves the kernel
 // instead of spinning for ever on a shared GPU.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = 200000u) {
