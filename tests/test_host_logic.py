@@ -71,6 +71,53 @@ def test_prefix_cache_hit_restore_and_aliasing():
     assert pc.stats["hits"] == 3 and pc.stats["inserted"] == 2
 
 
+def test_prefix_cache_pages_are_shared_not_copied():
+    """K/V lives in pages: a child shares its parent's full pages, a paged restore shares the checkpoint's full pages and copies
+    only the partly filled last one, and a live paged sequence is checkpointed without copying its full pages."""
+    pc = PrefixCache(budget_mb=64, page_size=64, kv_pages=64)
+    toks = np.arange(3000, 3400, dtype=np.int32)
+    st = _state(300, 320, 5)
+    n1 = pc.insert(None, toks, 160, st)                               # pages 0, 1 full, page 2 holds rows 128..159
+    pool = pc.pool
+    assert len(n1.pages) == 3 and n1.own == 3 and pool.available() == 63 - 3
+    n2 = pc.insert(n1, toks, 300, st)                                 # shares pages 0, 1; own pages for rows 128..299
+    assert n2.pages[:2] == n1.pages[:2] and n2.pages[2] != n1.pages[2] and len(n2.pages) == 5 and n2.own == 3
+    assert list(pool.refs[n1.pages[:2]]) == [2, 2] and pool.refs[n1.pages[2]] == 1
+    assert n2.kv.shape[3] == 140                                      # the reference's segment view: rows [160, 300)
+    dense, _ = pc.restore(n2, 320)
+    for (K, V), (K0, V0) in zip(dense["kv"], st["kv"]):
+        assert torch.equal(K[:, :, :300], K0[:, :, :300]) and torch.equal(V[:, :, :300], V0[:, :, :300]) and float(K[:, :, 300:].abs().max()) == 0
+    # paged restore: full pages by reference, the partial page by copy
+    live, chain = pc.restore_paged(n2)
+    assert [c.pos for c in chain] == [160, 300]
+    assert live["pages"][:4] == n2.pages[:4] and live["pages"][4] != n2.pages[4]
+    assert list(pool.refs[n2.pages[:2]]) == [3, 3] and pool.refs[live["pages"][4]] == 1
+    tail = live["pages"][4]
+    assert torch.equal(pool.K[0][tail, :, :300 - 256], pool.K[0][n2.pages[4], :, :300 - 256])
+    # the live sequence appends rows 300..319 to its own copy of the last page; the checkpoint's page is untouched
+    before = pool.K[0][n2.pages[4]].clone()
+    pool.K[0][tail, :, 300 - 256:] = 7
+    assert torch.equal(pool.K[0][n2.pages[4]], before)
+    # checkpoint the live sequence at 320 (page-aligned): nothing is copied, its five pages are shared
+    free_before = pool.available()
+    n3 = pc.insert(n2, np.concatenate([toks[:300], np.arange(20, dtype=np.int32)]), 320, {"pages": live["pages"], "conv": live["conv"], "ssm": live["ssm"]})
+    assert n3.pages == live["pages"] and pool.available() == free_before and pool.refs[tail] == 2 and n3.own == 1
+    pc.release_pages(live["pages"])
+    assert pool.refs[tail] == 1 and list(pool.refs[n1.pages[:2]]) == [3, 3]          # n1, n2, n3
+    pc.clear()
+    assert pool.available() == 63 and int(pool.refs.sum()) == 0
+
+
+def test_prefix_cache_page_pool_exhaustion_evicts_leaves():
+    pc = PrefixCache(budget_mb=512, page_size=64, kv_pages=7)          # 6 usable pages
+    a = pc.insert(None, np.arange(0, 200, dtype=np.int32), 192, _state(192, 256, 1))       # 3 pages
+    b = pc.insert(None, np.arange(1000, 1200, dtype=np.int32), 192, _state(192, 256, 2))   # 3 pages: pool full
+    assert pc.pool.available() == 0
+    c = pc.insert(None, np.arange(2000, 2200, dtype=np.int32), 128, _state(128, 256, 3))   # needs 2: the LRU leaf (a) goes
+    assert c is not None and a.uid not in pc.nodes and b.uid in pc.nodes and pc.stats["evicted"] == 1
+    assert pc.insert(None, np.arange(5000, 5600, dtype=np.int32), 512, _state(512, 512, 4)) is None, "8 pages can never fit"
+
+
 def test_prefix_cache_split_learning_and_identical_insert():
     pc = PrefixCache(budget_mb=64)
     a = np.arange(0, 200, dtype=np.int32)
