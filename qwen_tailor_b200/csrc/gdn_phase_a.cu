@@ -54,8 +54,8 @@ __device__ __forceinline__ void pa_split_pack(float x0, float x1, uint32_t& hi, 
 // bounded wait with a pause between polls
 __device__ __forceinline__ bool pa_wait(uint32_t bar, uint32_t parity) {
     for (uint32_t i = 0; i < PA_WAIT_LIMIT; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        __nanosleep(100);
+        if (mbar_test_wait(bar, parity)) return true;
+        __nanosleep(40);
     }
     return false;
 }

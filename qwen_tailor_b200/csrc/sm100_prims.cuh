@@ -21,8 +21,8 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// One poll: the thread is suspended by the hardware until the phase completes or ~`hint_ns` have passed, so a waiting warp
-// does not compete for issue slots with the warps that do the work.
+// One suspending poll: the hardware may park the thread until the phase completes or ~`hint_ns` have passed.  On this part a call
+// costs ~250 cycles even when the phase completed long ago (measured), so the waits below use the non-blocking form.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns = 20000u) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -36,14 +36,13 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls and returns false.  The caller records the failure and leaves the kernel
-// instead of spinning for ever on a shared GPU.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = 200000u) {
+// Bounded wait: non-blocking polls with a ~20 ns pause in between (back-to-back polls would take issue slots from the warps that
+// do the work); gives up after `limit` polls and returns false.  The caller records the failure and leaves the kernel instead
+// of spinning for ever on a shared GPU.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = 2000000u) {
     for (uint32_t i = 0; i < limit; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-#ifdef GDN_POLL_SLEEP
-        __nanosleep(GDN_POLL_SLEEP);
-#endif
+        if (mbar_test_wait(bar, parity)) return true;
+        __nanosleep(20);
     }
     return false;
 }
