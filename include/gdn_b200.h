@@ -25,6 +25,13 @@
 extern "C" {
 #endif
 
+/* The library is built with hidden visibility; only the entry points declared here are exported. */
+#if defined(__GNUC__)
+#define GDN_API __attribute__((visibility("default")))
+#else
+#define GDN_API
+#endif
+
 #define GDN_OK 0
 #define GDN_E_SHAPE (-1)
 #define GDN_E_DTYPE (-2)
@@ -36,10 +43,10 @@ extern "C" {
 #define GDN_E_NULL (-8)
 
 /* Library version (major*10000 + minor*100 + patch). */
-int gdn_version(void);
+GDN_API int gdn_version(void);
 
 /* Message of the last error returned to the calling thread ("" if none). */
-const char* gdn_last_error_string(void);
+GDN_API const char* gdn_last_error_string(void);
 
 /* Reads (and clears) the current device's status word.  Synchronises the device.  Values (the last event wins):
  *   0  every device-side check passed since the last call
@@ -49,26 +56,26 @@ const char* gdn_last_error_string(void);
  *   3  a bounded wait inside a prefill kernel gave up; the block left early
  *   4  a kernel found its dynamic shared memory not 1024-byte aligned and did nothing
  * None of these faults the device: the context stays usable and the affected outputs are left unwritten or undefined. */
-int gdn_device_status(int* status_host);
+GDN_API int gdn_device_status(int* status_host);
 
 /* compute_g and beta = sigmoid(b) with the reference's bf16 rounding points.
  * Replaces: compute_g, qwen35/gated_delta.py:16-18; beta at qwen35/gated_delta.py:158; kernel form qwen35/kernels.py:511-515.
  *   a, b     bf16, element (row r, head h) at a[r*a_stride + h] / b[r*b_stride + h]   (either may be NULL)
  *   A_log, dt_bias   fp32 [H]
  *   g, lg, beta      fp32 [n_rows, H] outputs: decay exp(lg), log-decay, beta           (any may be NULL) */
-int gdn_gates(const void* a, const void* b, long long a_stride, long long b_stride, const float* A_log, const float* dt_bias,
+GDN_API int gdn_gates(const void* a, const void* b, long long a_stride, long long b_stride, const float* A_log, const float* dt_bias,
               float* g, float* lg, float* beta, long long n_rows, int H, void* stream);
 
 /* q <- l2norm(q) * inv_scale^2, k <- l2norm(k) * inv_scale over rows of 128 bf16.
  * Replaces: normalize_qk, qwen35/gated_delta.py:21-30 (kernel form qwen35/kernels.py:490-509). */
-int gdn_normalize_qk(const void* q, const void* k, void* q_out, void* k_out, long long n_rows, float inv_scale, float eps, void* stream);
+GDN_API int gdn_normalize_qk(const void* q, const void* k, void* q_out, void* k_out, long long n_rows, float inv_scale, float eps, void* stream);
 
 /* Sequential gated delta rule over T tokens.
  * Replaces: gated_delta_update's kernel, qwen35/gated_delta.py:33-137,167-174.
  *   q, k  bf16 [B,T,Hk,128];  v bf16 [B,T,Hv,Dv];  g, beta fp32 [B,T,Hv];  state_in fp32 [B,Hv,Dv,128] or NULL (zeros)
  *   y     bf16 [B,T,Hv,Dv];   state_out fp32 [B,Hv,Dv,128]
  * Errors: GDN_E_SHAPE unless Dk == 128, Dv % 16 == 0 and Hv % Hk == 0 (the reference raises ValueError, gated_delta.py:164-166). */
-int gdn_recurrent(const void* q, const void* k, const void* v, const float* g, const float* beta, const float* state_in, void* y,
+GDN_API int gdn_recurrent(const void* q, const void* k, const void* v, const float* g, const float* beta, const float* state_in, void* y,
                   float* state_out, int B, int T, int Hk, int Hv, int Dk, int Dv, void* stream);
 
 /* Chunked prefill (chunk 64, tcgen05 tensor cores) over a packed varlen batch, with optional resume from a cached state:
@@ -84,19 +91,19 @@ int gdn_recurrent(const void* q, const void* k, const void* v, const float* g, c
  *   workspace: gdn_prefill_workspace_bytes(n_seq, total_T, H) bytes, 16-byte aligned: the phase-A records between the two kernels
  *   heads [head_lo, head_hi) are computed (head-group sharding of one long sequence); the others are not touched
  * Errors: GDN_E_SHAPE for bad sizes or a short workspace, GDN_E_ALIGN, GDN_E_UNSUPPORTED if the driver lacks tensor-map support. */
-int gdn_prefill_chunked(const void* q, const void* k, const void* v, const float* lg, const float* beta, const int* cu_seqlens,
+GDN_API int gdn_prefill_chunked(const void* q, const void* k, const void* v, const float* lg, const float* beta, const int* cu_seqlens,
                         const float* init_state, const int* init_idx, void* y, float* final_state, void* workspace, size_t workspace_bytes,
                         int n_seq, long long total_T, int H, int head_lo, int head_hi, void* stream);
 
 /* Bytes of the phase-A record buffer for a packed batch: (total_T / 64 + n_seq) * H records of 17,152 bytes (Tb as bf16 hi + lo
  * operand images, and the chunk's cumulative log-decay, gamma and dec vectors).  Stands in for the reference's Tbuf / Abuf / gv
  * outputs of phase A (qwen35/gdn_nax.py:394-401,420-422). */
-size_t gdn_prefill_workspace_bytes(int n_seq, long long total_T, int H);
+GDN_API size_t gdn_prefill_workspace_bytes(int n_seq, long long total_T, int H);
 
 /* Phase A: the state-independent part of every 64-token chunk, one independent tile per (chunk, head) -- cumulative decay,
  * K K^T on the tensor cores, the exact inverse (I + L)^-1 and Tb = T diag(beta) -- written as records for phase B.
  * Replaces: the reference's phase-A kernel gdn_nax_a, qwen35/gdn_nax.py:71-143 (launched at :420-422). */
-int gdn_phase_a(const void* k, const float* lg, const float* beta, const int* cu_seqlens, void* records, size_t records_bytes, int n_seq,
+GDN_API int gdn_phase_a(const void* k, const float* lg, const float* beta, const int* cu_seqlens, void* records, size_t records_bytes, int n_seq,
                 long long total_T, int H, int head_lo, int head_hi, void* stream);
 
 /* Phase A fused with the prefill front end: reads the in_proj rows once, computes conv (4 taps) + silu, q / k l2norm (q also scaled
@@ -105,13 +112,13 @@ int gdn_phase_a(const void* k, const float* lg, const float* beta, const int* cu
  * Replaces: prep_a, qwen35/gdn_nax.py:394-401 (kernel :150-222), the reference's default prefill path (qwen35/prefill.py:251-252).
  *   proj bf16 [total_T, row_stride >= 8224];  conv_state bf16 [n_seq, 3, 6144]: the three raw rows before each sequence
  *   conv_w bf16 [6144*4];  A_log, dt_bias fp32 [16];  q, k, v bf16 [total_T, 16, 128] outputs */
-int gdn_prep_a(const void* proj, long long row_stride, const void* conv_state, const void* conv_w, const float* A_log, const float* dt_bias,
+GDN_API int gdn_prep_a(const void* proj, long long row_stride, const void* conv_state, const void* conv_w, const float* A_log, const float* dt_bias,
                const int* cu_seqlens, void* q, void* k, void* v, void* records, size_t records_bytes, int n_seq, long long total_T, int head_lo,
                int head_hi, void* stream);
 
 /* Phase B: the serial chain over the chunks of every (sequence, head), fp32 state resident in tensor memory.
  * Replaces: phase_b, qwen35/gdn_nax.py:404-410 (kernel gdn_nax_b :224-358), called at qwen35/prefill.py:253. */
-int gdn_phase_b(const void* q, const void* k, const void* v, const void* records, size_t records_bytes, const int* cu_seqlens,
+GDN_API int gdn_phase_b(const void* q, const void* k, const void* v, const void* records, size_t records_bytes, const int* cu_seqlens,
                 const float* init_state, const int* init_idx, void* y, float* final_state, int n_seq, long long total_T, int H, int head_lo,
                 int head_hi, void* stream);
 
@@ -120,7 +127,7 @@ int gdn_phase_b(const void* q, const void* k, const void* v, const void* records
  *   proj bf16 [M, row_stride>=8224];  conv_snap bf16 [n_snap,3,6144];  conv_w bf16 [6144*4];  ssm_snap fp32 [n_snap,16,128,128]
  *   sel int32[1] (device): snapshot the call starts from
  *   y bf16 [M,2048];  conv_out bf16 [M,3,6144];  ssm_out fp32 [M,16,128,128]   (snapshot j = state after token j) */
-int gdn_deltanet(const void* proj, long long row_stride, const void* conv_snap, const void* conv_w, const float* A_log,
+GDN_API int gdn_deltanet(const void* proj, long long row_stride, const void* conv_snap, const void* conv_w, const float* A_log,
                  const float* dt_bias, const float* ssm_snap, const int* sel, int n_snap, void* y, void* conv_out, float* ssm_out,
                  int M, void* stream);
 
@@ -128,7 +135,7 @@ int gdn_deltanet(const void* proj, long long row_stride, const void* conv_snap, 
  * Replaces: deltanet_b, qwen35/batch.py:128-135 (kernel :36-127).
  *   conv_pool bf16 [n_slots*2,3,6144] (reads buffer pos&1 of the slot, writes the other);  ssm_pool fp32 [n_slots,16,128,128]
  *   slots, pos int32 [B] (device);  y bf16 [B,2048] */
-int gdn_deltanet_b(const void* proj, long long row_stride, void* conv_pool, const void* conv_w, const float* A_log, const float* dt_bias,
+GDN_API int gdn_deltanet_b(const void* proj, long long row_stride, void* conv_pool, const void* conv_w, const float* A_log, const float* dt_bias,
                    float* ssm_pool, const int* slots, const int* pos, int n_slots, void* y, int B, void* stream);
 
 /* Batched speculative verify, M chained tokens for each of B sequences over snapshot pools, in place.
@@ -136,12 +143,12 @@ int gdn_deltanet_b(const void* proj, long long row_stride, void* conv_pool, cons
  *   conv_pool bf16 [n_entries*2, M, 3, 6144];  ssm_pool fp32 [n_entries, M, 16,128,128]
  *   sslots, sels, pars int32 [B] (device): pool entry, start snapshot, conv buffer read (the other one is written)
  *   proj bf16 [B*M, row_stride];  y bf16 [B*M,2048] */
-int gdn_deltanet_bm(const void* proj, long long row_stride, void* conv_pool, const void* conv_w, const float* A_log, const float* dt_bias,
+GDN_API int gdn_deltanet_bm(const void* proj, long long row_stride, void* conv_pool, const void* conv_w, const float* A_log, const float* dt_bias,
                     float* ssm_pool, const int* sslots, const int* sels, const int* pars, int n_entries, void* y, int B, int M,
                     void* stream);
 
 /* Bytes of fp32 workspace gqa_decode_paged needs for B sequences whose contexts are at most max_ctx tokens. */
-size_t gqa_decode_workspace_bytes(int B, int max_ctx);
+GDN_API size_t gqa_decode_workspace_bytes(int B, int max_ctx);
 
 /* GQA decode attention (8 query heads, 2 KV heads, head_dim 256) over a paged bf16 KV cache, M <= 4 chained rows per
  * sequence, new K/V rows appended in place.
@@ -151,7 +158,7 @@ size_t gqa_decode_workspace_bytes(int B, int max_ctx);
  *   k_pages, v_pages bf16 [n_pages,2,page_size,256];  block_table int32 [B,max_pages];  ctx_len int32 [B] (tokens cached)
  *   out bf16 [B*M,8,256];  workspace: at least gqa_decode_workspace_bytes(B, max_ctx) bytes, 16-byte aligned (GDN_E_SHAPE otherwise)
  *   max_ctx: host-side upper bound of ctx_len (informational: the work split is derived from ctx_len on the device) */
-int gqa_decode_paged(const void* q, const void* k_new, const void* v_new, void* k_pages, void* v_pages, const int* block_table,
+GDN_API int gqa_decode_paged(const void* q, const void* k_new, const void* v_new, void* k_pages, void* v_pages, const int* block_table,
                      const int* ctx_len, void* out, void* workspace, size_t workspace_bytes, int B, int M, int page_size,
                      int max_pages, int n_pages, int max_ctx, void* stream);
 
@@ -168,7 +175,7 @@ int gqa_decode_paged(const void* q, const void* k_new, const void* v_new, void* 
  *          first call outside any stream capture.
  *   Sharing: all calls on a device use the same array, which keeps the previous call's contents.  Nothing in it needs
  *          clearing between calls, but two calls that run concurrently on one GPU (different streams) corrupt each other. */
-int gqa_decode_paged_static(const void* q, const void* k_new, const void* v_new, void* k_pages, void* v_pages, const int* block_table,
+GDN_API int gqa_decode_paged_static(const void* q, const void* k_new, const void* v_new, void* k_pages, void* v_pages, const int* block_table,
                             const int* ctx_len, void* out, int B, int M, int page_size, int max_pages, int n_pages, int max_ctx,
                             void* stream);
 
@@ -178,28 +185,28 @@ int gqa_decode_paged_static(const void* q, const void* k_new, const void* v_new,
  *   qkv bf16 [R, row_stride >= 5120] (8 x (q 256 | gate 256), k 2 x 256, v 2 x 256);  q_norm, k_norm fp32 [256] (the "+1" of
  *   the checkpoint already folded in, qwen35/model.py:95-96);  row_pos int32 [R] position of every row
  *   q bf16 [R,8,256], gate bf16 [R,8,256], k, v bf16 [R,2,256] */
-int gqa_qkv_prep(const void* qkv, long long row_stride, const float* q_norm, const float* k_norm, const int* row_pos, void* q, void* gate, void* k,
+GDN_API int gqa_qkv_prep(const void* qkv, long long row_stride, const float* q_norm, const float* k_norm, const int* row_pos, void* q, void* gate, void* k,
                  void* v, int R, float eps, float rope_theta, void* stream);
 
 /* out = o * sigmoid(gate), elementwise over n bf16 values (n % 4 == 0).  Replaces: qwen35/fast.py:84, qwen35/batch.py:512. */
-int gqa_gate_out(const void* o, const void* gate, void* out, long long n, void* stream);
+GDN_API int gqa_gate_out(const void* o, const void* gate, void* out, long long n, void* stream);
 
 /* Prefill front end of a GDN layer: depthwise causal conv (4 taps) + silu on the mixed qkv columns of proj, q/k l2norm (q also
  * scaled by 128^-1/2), and the new conv window (last 3 raw rows).
  * Replaces: conv_prep, qwen35/prefill.py:96-134,160-238; window update qwen35/prefill.py:262-263.
  *   proj bf16 [S, row_stride >= 8224];  conv_state bf16 [3,6144];  conv_w bf16 [6144*4]
  *   q, k, v bf16 [S,16,128];  new_conv bf16 [3,6144] (must not alias conv_state) */
-int gdn_conv_prep(const void* proj, long long row_stride, const void* conv_state, const void* conv_w, void* q, void* k, void* v, void* new_conv,
+GDN_API int gdn_conv_prep(const void* proj, long long row_stride, const void* conv_state, const void* conv_w, void* q, void* k, void* v, void* new_conv,
                   int S, void* stream);
 
 /* Gated RMSNorm on the GDN output: out = silu(z) * w * y * rsqrt(mean(y^2) + 1e-6) per (token, head), z = proj[:, 6144:8192].
  * Replaces: gated_norm, qwen35/prefill.py:137-157,241-244.
  *   y bf16 [S,2048];  proj bf16 [S, row_stride >= 8224];  gw fp32 [128];  out bf16 [S,2048] */
-int gdn_gated_norm(const void* y, const void* proj, long long row_stride, const float* gw, void* out, long long S, void* stream);
+GDN_API int gdn_gated_norm(const void* y, const void* proj, long long row_stride, const float* gw, void* out, long long S, void* stream);
 
 /* dst.flat[d0 + y*dstride + i] = src.flat[s0 + y*sstride + i] for i < n, y < ny; offsets in elements of elem_size (2 or 4) bytes.
  * Replaces: blit, qwen35/batch.py:349-372. */
-int gdn_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,
+GDN_API int gdn_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,
                    long long sstride, void* stream);
 
 #ifdef __cplusplus

@@ -450,7 +450,7 @@ int launch_phase_a(const void* k, const PhaseAArgs& a, bool fused, cudaStream_t 
 }  // namespace gdn
 
 #ifdef GDN_TIMING
-extern "C" int gdn_timing_log_a(long long* out_host, int n) {
+extern "C" __attribute__((visibility("default"))) int gdn_timing_log_a(long long* out_host, int n) {
     return cudaMemcpyFromSymbol(out_host, gdn::g_tlog, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
 }
 #endif

@@ -613,7 +613,7 @@ int launch_phase_b(const void* q, const void* k, const void* v, const PrefillArg
 }  // namespace gdn
 
 #ifdef GDN_TIMING
-extern "C" int gdn_timing_log_b(long long* out_host, int n) {
+extern "C" __attribute__((visibility("default"))) int gdn_timing_log_b(long long* out_host, int n) {
     return cudaMemcpyFromSymbol(out_host, gdn::g_tlog, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
 }
 #endif

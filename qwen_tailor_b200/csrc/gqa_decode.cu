@@ -15,9 +15,10 @@
 //     block's range is stored directly.
 //   * GQA packing: the 4 query heads of a KV head times the M <= 4 chained rows form the 16 rows of a warp-level
 //     m16n8k16 bf16 MMA, so each K/V byte is read once for up to 16 query rows (at M = 4 plain FMAs could not keep up with
-//     HBM).  The 8 warps are 4 key groups x 2 halves of the head dim: a warp computes the scores of its 16 keys of a tile
-//     (both warps of a pair do, it is cheap) and P.V for its 128 of the 256 dims, with its own online-softmax state; eight
-//     warps rather than four because the per-tile dependency chains are latency-bound and need other warps to hide behind.
+//     HBM).  The 8 warps are 4 key groups x 2 halves of the head dim: a warp computes the scores of 8 of its group's 16 keys,
+//     swaps them with its partner through shared memory (warp-level MMAs run at a fraction of the tcgen05 rate on this part and
+//     the kernel is bound by their number, so nothing is computed twice), and does P.V for its 128 of the 256 dims with its own
+//     online-softmax state.
 //   * K/V tiles (64 keys x 512 B) are gathered page by page with 16-byte cp.async into XOR-swizzled shared memory, three
 //     stages (192 KiB per SM, two tiles in flight while one is consumed).  The page lookup of a tile's 64 keys is done once
 //     (one thread per key) and shared through shared memory.
@@ -37,7 +38,8 @@ constexpr int ATT_THREADS = 256, KGROUPS = 4, KPW = TK / KGROUPS;      // 4 key 
 constexpr int ROWB = ATT_D * 2;                 // bytes per key row (512)
 constexpr int TILE_BYTES = TK * ROWB;           // 32 KiB
 constexpr int ATT_STAGES = 3;
-constexpr int ATT_SMEM = 16 * ROWB + ATT_STAGES * 2 * TILE_BYTES + ATT_STAGES * TK * 8;     // Q (8 KiB) + stages x (K + V) + row offsets
+constexpr int ATT_XCHG = 2 * KGROUPS * 2 * 32 * 16;                     // score exchange between the two warps of a key group, two buffers
+constexpr int ATT_SMEM = 16 * ROWB + ATT_STAGES * 2 * TILE_BYTES + ATT_STAGES * TK * 8 + ATT_XCHG;     // Q (8 KiB) + stages x (K + V) + row offsets + exchange
 constexpr int PART_STRIDE = 16 * ATT_D + 32;    // floats per (sequence, kv head, split): O[16][256] + (m, l)[16]
 
 
@@ -338,16 +340,33 @@ gqa_decode_split_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tm
                 sm100::fence_proxy_async_smem();                     // these generic writes precede the next tensor-map copy into the stage
                 __syncwarp();
             }
+            // scores of this warp's 8 keys (16 kg + 8 dh ..): one K fragment load covers two 16-dim steps
             float sc2[2][4];
+            {
+                // four independent accumulators: the sixteen 16-dim steps form four chains of four dependent MMAs instead of one of sixteen
+                float acc4[4][4];
 #pragma unroll
-            for (int n = 0; n < 2; n++) { sc2[n][0] = sc2[n][1] = sc2[n][2] = sc2[n][3] = 0.f; }
+                for (int i = 0; i < 4; i++) { acc4[i][0] = acc4[i][1] = acc4[i][2] = acc4[i][3] = 0.f; }
 #pragma unroll
-            for (int ks = 0; ks < 16; ks++) {
-                uint32_t af[4], bfr[4];
-                ldsm_x4(sQ + swz((lane & 7) + 8 * ((lane >> 3) & 1), 2 * ks + (lane >> 4)), af);
-                ldsm_x4(tK + kvoff(kg * KPW + (lane & 7) + 8 * (lane >> 4), 2 * ks + ((lane >> 3) & 1)), bfr);
-                mma_bf16(sc2[0], af, bfr[0], bfr[1]);
-                mma_bf16(sc2[1], af, bfr[2], bfr[3]);
+                for (int kp = 0; kp < 8; kp++) {
+                    uint32_t bfr[4], af[4];
+                    ldsm_x4(tK + kvoff(kg * KPW + 8 * dh + (lane & 7), 4 * kp + (lane >> 3)), bfr);
+                    ldsm_x4(sQ + swz((lane & 7) + 8 * ((lane >> 3) & 1), 4 * kp + (lane >> 4)), af);
+                    mma_bf16(acc4[(2 * kp) & 3], af, bfr[0], bfr[1]);
+                    ldsm_x4(sQ + swz((lane & 7) + 8 * ((lane >> 3) & 1), 4 * kp + 2 + (lane >> 4)), af);
+                    mma_bf16(acc4[(2 * kp + 1) & 3], af, bfr[2], bfr[3]);
+                }
+                float own[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) own[e] = (acc4[0][e] + acc4[1][e]) + (acc4[2][e] + acc4[3][e]);
+                // swap with the partner warp (same key group, other half of the dims): it holds the group's other 8 keys
+                float4* xb = reinterpret_cast<float4*>(smem + 16 * ROWB + ATT_STAGES * 2 * TILE_BYTES + ATT_STAGES * TK * 8) + ((t & 1) * KGROUPS + kg) * 64;
+                xb[dh * 32 + lane] = make_float4(own[0], own[1], own[2], own[3]);
+                asm volatile("bar.sync %0, 64;" ::"r"(2 + kg) : "memory");
+                const float4 oth = xb[(dh ^ 1) * 32 + lane];
+                const float ot[4] = {oth.x, oth.y, oth.z, oth.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) { sc2[0][e] = dh ? ot[e] : own[e]; sc2[1][e] = dh ? own[e] : ot[e]; }
             }
             // mask + online softmax; thread holds rows g (e = 0,1) and g + 8 (e = 2,3), keys 16*kg + 8n + 2*t4 + (e & 1)
             float mx[2] = {-INFINITY, -INFINITY};
