@@ -51,8 +51,12 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 #ifdef GDN_TIMING
 static __device__ long long g_tlog[8192];
 #define GDN_TSTAMP(slot) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (slot) < 8192) g_tlog[(slot)] = clock64(); } while (0)
+// per-block stamps on the global nanosecond timer: slot 4096 + 8 * block + k
+__device__ __forceinline__ long long gdn_globaltimer() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+#define GDN_BSTAMP(k) do { if (threadIdx.x == 0 && blockIdx.x < 500) g_tlog[4096 + 8 * blockIdx.x + (k)] = gdn_globaltimer(); } while (0)
 #else
 #define GDN_TSTAMP(slot) do { } while (0)
+#define GDN_BSTAMP(k) do { } while (0)
 #endif
 
 __device__ __forceinline__ float warp_sum(float v) {
