@@ -50,13 +50,20 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 // unit's own g_tlog, which that unit's gdn_timing_log_* function copies out.
 #ifdef GDN_TIMING
 static __device__ long long g_tlog[8192];
-#define GDN_TSTAMP(slot) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && (slot) < 8192) g_tlog[(slot)] = clock64(); } while (0)
-// per-block stamps on the global nanosecond timer: slot 4096 + 8 * block + k
+#ifndef GDN_TBLOCK
+#define GDN_TBLOCK 0
+#endif
+#define GDN_TSTAMP(slot) do { if (blockIdx.x == GDN_TBLOCK && (threadIdx.x & 31) == 0 && (slot) < 8192) g_tlog[(slot)] = clock64(); } while (0)
+// per-block stamps on the global nanosecond timer: slot 4096 + 16 * block + k
 __device__ __forceinline__ long long gdn_globaltimer() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#define GDN_BSTAMP(k) do { if (threadIdx.x == 0 && blockIdx.x < 500) g_tlog[4096 + 8 * blockIdx.x + (k)] = gdn_globaltimer(); } while (0)
+#define GDN_BSTAMP_ANY(k) do { if (blockIdx.x < 250) g_tlog[4096 + 16 * blockIdx.x + (k)] = gdn_globaltimer(); } while (0)
+#define GDN_BVAL(k, v) do { if (threadIdx.x == 0 && blockIdx.x < 250) g_tlog[4096 + 16 * blockIdx.x + (k)] = (long long)(v); } while (0)
+#define GDN_BSTAMP(k) do { if (threadIdx.x == 0 && blockIdx.x < 250) g_tlog[4096 + 16 * blockIdx.x + (k)] = gdn_globaltimer(); } while (0)
 #else
 #define GDN_TSTAMP(slot) do { } while (0)
 #define GDN_BSTAMP(k) do { } while (0)
+#define GDN_BVAL(k, v) do { } while (0)
+#define GDN_BSTAMP_ANY(k) do { } while (0)
 #endif
 
 __device__ __forceinline__ float warp_sum(float v) {

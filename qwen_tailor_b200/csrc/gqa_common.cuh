@@ -59,6 +59,7 @@ __device__ __forceinline__ int block_of_tile(long long i, int G, long long N) { 
 
 // the tcgen05 kernel (gqa_decode_tc.cu)
 constexpr int TC_THREADS = 128;
+constexpr int TC_MAX_PAIRS = 512;                                        // (sequence, KV head) pairs the kernel plans for in shared memory
 constexpr int TC_Q_BYTES = 16384;                                      // Q operand: 4 slabs of 32 rows x 128 B (the 16 query rows, twice)
 constexpr int TC_SMEM = TC_Q_BYTES + ATT_STAGES * 2 * TILE_BYTES;      // + three stages of K + V tiles
 int launch_gqa_decode_tc(const AttnArgs& a, const CUtensorMap& tk, const CUtensorMap& tv, cudaStream_t stream);

@@ -41,7 +41,9 @@ __global__ void __launch_bounds__(256) gqa_decode_plan_kernel(const AttnArgs a) 
     auto tiles_of = [&](int p) -> int {
         const int ctx = a.ctx_len[p / ATT_KV];
         if (ctx < 0 || (long long)ctx + a.M > (long long)a.max_pages * a.page_size) { atomicExch(a.status, 1); return 0; }
-        return (ctx + TK - 1) / TK + 1;                               // cached keys + one tile for the rows of this call
+        // cached keys + one tile for the rows of this call + the weight of the pair's epilogue: `tail_tiles` tiles without work,
+        // so that a block that finishes a pair (reads out the accumulator, maybe merges) is given that much less to stream
+        return (ctx + TK - 1) / TK + 1 + a.tail_tiles;
     };
     auto scan = [&](int local) -> int {                               // exclusive prefix of `local` over the block
         int x = local;
@@ -66,10 +68,11 @@ __global__ void __launch_bounds__(256) gqa_decode_plan_kernel(const AttnArgs a) 
     // so the blocks of a pair are consecutive and each of its partial slots is written
     const int G = (int)min((long long)a.G, max(N, 1ll));
     if (tid == 0) a.meta[1] = G;
+    // a pair's partials come from the blocks that hold its tiles with work (the weight tiles at its end carry none)
     local = 0;
     for (int p = p0; p < p1; p++) {
         const int t = cum[p + 1] - cum[p];
-        local += t > 0 ? block_of_tile(cum[p + 1] - 1, G, N) - block_of_tile(cum[p], G, N) + 1 : 0;
+        local += t > 0 ? block_of_tile(cum[p + 1] - 1 - a.tail_tiles, G, N) - block_of_tile(cum[p], G, N) + 1 : 0;
     }
     run = scan(local);
     for (int p = p0; p < p1; p++) {
@@ -77,7 +80,7 @@ __global__ void __launch_bounds__(256) gqa_decode_plan_kernel(const AttnArgs a) 
         const int f = t > 0 ? block_of_tile(cum[p], G, N) : 0;
         first[p] = f;
         base[p] = run;
-        run += t > 0 ? block_of_tile(cum[p + 1] - 1, G, N) - f + 1 : 0;
+        run += t > 0 ? block_of_tile(cum[p + 1] - 1 - a.tail_tiles, G, N) - f + 1 : 0;
     }
     if (tid == min(255, (P - 1) / max(chunk, 1))) base[P] = run;
     int* count = meta_count(a.meta, P);
@@ -543,16 +546,21 @@ static int launch_with_workspace(AttnArgs a, void* ws, size_t ws_bytes, const ch
             return check_launch("gqa_decode smem attribute");
         attr_set[dev] = true;
     }
-    gqa_decode_plan_kernel<<<1, 256, 0, stream>>>(a);
-    int rc = check_launch("gqa_decode_plan");
-    if (rc) return rc;
     // pages that hold a multiple of 64 keys: every 64-key tile lies inside one page and can be fetched by tensor-map copies
     CUtensorMap tk, tv;
     memset(&tk, 0, sizeof(tk));
     memset(&tv, 0, sizeof(tv));
     bool tma = a.page_size % TK == 0 && make_page_map(&tk, a.k_pages, a.page_size, a.n_pages) && make_page_map(&tv, a.v_pages, a.page_size, a.n_pages);
-    if (tma) return launch_gqa_decode_tc(a, tk, tv, stream);         // tcgen05 path
-    gqa_decode_split_kernel<false><<<a.G, ATT_THREADS, ATT_SMEM, stream>>>(a, tk, tv);
+    if (tma && a.P <= TC_MAX_PAIRS) {                                // tcgen05 path: plans for itself
+        a.tail_tiles = 2;
+        return launch_gqa_decode_tc(a, tk, tv, stream);
+    }
+    a.tail_tiles = 0;
+    gqa_decode_plan_kernel<<<1, 256, 0, stream>>>(a);
+    int rc = check_launch("gqa_decode_plan");
+    if (rc) return rc;
+    if (tma) gqa_decode_split_kernel<true><<<a.G, ATT_THREADS + 32, ATT_SMEM, stream>>>(a, tk, tv);
+    else gqa_decode_split_kernel<false><<<a.G, ATT_THREADS, ATT_SMEM, stream>>>(a, tk, tv);
     return check_launch("gqa_decode_split");
 }
 

@@ -16,8 +16,16 @@
 // 2^8 (P then stays below 256, far inside bf16 / fp32 range), which makes the rescale of O -- a round trip through registers --
 // rare; the final result is exact either way because l and O carry the same reference.
 //
-// Roles (128 threads, one persistent block per SM): warp 0 softmax / epilogue (lanes 0..15 own the query rows), warp 1 lane 0
-// issues the MMAs, warp 2 is the TMA producer (three-stage ring of K + V tiles), warp 3 stages Q and appends the new rows.
+// Roles (128 threads, one persistent block per SM): warp 0 softmax / epilogue (lanes r and r + 16 share query row r), warp 1 lane 0
+// issues the MMAs, warp 2 is the TMA producer (three-stage ring of K + V tiles; it runs ahead on its own through all the pairs of
+// the block's range, and marks the cache lines evict-first so that the stream does not flush everything else out of L2), warp 3
+// stages Q and appends the new rows -- for the block's next pair while the current one streams, because a plain load issued
+// while the copies saturate the memory system takes microseconds.
+//
+// There is no plan kernel in front of this one: every block derives the balanced split from the context lengths itself.  The
+// blocks of a pair meet at an arrival counter in the workspace; the one that arrives last merges the pair's partials, which it
+// fetches with bulk copies into the (then idle) ring when the pair is the block's last.  The counters carry an epoch tag and need
+// no zeroing, see `touch` / `arrive` below.
 // Every wait is bounded; a wait that gives up sets the device status word and the block runs out its loops without touching
 // the tensor cores again.
 #include <cstring>
@@ -29,8 +37,88 @@ namespace gdn {
 using namespace sm100;
 
 constexpr uint32_t TCM_O = 0, TCM_S0 = 256, TCM_P0 = 384;            // O [256], S buffers [64] x 2, P buffers [hi 32 | lo 32] x 2
-enum { TB_FULL0 = 0, TB_EMPTY0 = 3, TB_SDONE0 = 6, TB_SFREE0 = 8, TB_PREADY0 = 10, TB_PFREE0 = 12, TB_ODONE = 14, TB_COUNT = 15 };
+enum { TB_FULL0 = 0, TB_EMPTY0 = 3, TB_SDONE0 = 6, TB_SFREE0 = 8, TB_PREADY0 = 10, TB_PFREE0 = 12, TB_ODONE = 14, TB_MERGE = 15, TB_COUNT = 16 };
+constexpr int TC_RING_PARTIALS = ATT_STAGES * 2 * TILE_BYTES / (PART_STRIDE * 4);      // partial images the idle ring can hold (11)
 constexpr float TC_RESCALE_STEP = 8.f;                               // log2 units
+
+// Weighted sum of the partials of a pair (the standard split-softmax merge): nsp images of PART_STRIDE floats at pb, in global
+// memory (read through L2) or, SM = true, already copied into shared memory.  Run by the 96 consumer threads.
+template <bool SM>
+__device__ __forceinline__ void tc_merge_pair(const float* pb, int nsp, float* s_w, float* s_l, __nv_bfloat16* out_pair, int M, int ctid) {
+    auto csync = [&]() { asm volatile("bar.sync 1, 96;" ::: "memory"); };
+    for (int i = ctid; i < nsp * 16; i += 96) {
+        const float2* src = reinterpret_cast<const float2*>(pb + (size_t)(i >> 4) * PART_STRIDE + 16 * ATT_D + 2 * (i & 15));
+        const float2 ml = SM ? *src : __ldcg(src);
+        s_w[i] = ml.x;
+        s_l[i] = ml.y;
+    }
+    csync();
+    {
+        // weights: thread (row, group of partials) -- six threads share a row's partials, the row's maximum and sum go through s_red
+        const int r = ctid & 15, g = ctid >> 4;
+        float* s_red = s_l + nsp * 16;                               // [6][16] maxima, then [6][16] sums
+        float mx = -INFINITY;
+        for (int sp = g; sp < nsp; sp += 6) mx = fmaxf(mx, s_w[sp * 16 + r]);
+        s_red[g * 16 + r] = mx;
+        csync();
+        float ms = s_red[r];
+#pragma unroll
+        for (int k = 1; k < 6; k++) ms = fmaxf(ms, s_red[k * 16 + r]);
+        float lsum = 0.f;
+        for (int sp = g; sp < nsp; sp += 6) {
+            const float m = s_w[sp * 16 + r];
+            const float w = (m == -INFINITY) ? 0.f : exp2f(m - ms);
+            lsum += w * s_l[sp * 16 + r];
+            s_w[sp * 16 + r] = w;
+        }
+        s_red[96 + g * 16 + r] = lsum;
+        csync();
+        if (g == 0) {
+            float t = 0.f;
+#pragma unroll
+            for (int k = 0; k < 6; k++) t += s_red[96 + k * 16 + r];
+            s_w[nsp * 16 + r] = t == 0.f ? 1.f : 1.f / t;            // sum == 0 guard as qwen35/batch.py:216
+        }
+    }
+    csync();
+    GDN_BSTAMP(15);
+    // thread = (row, four dims), four of them at a time (independent loads and sums): neighbouring threads read neighbouring
+    // 16-byte words, every partial is an independent load
+    const int n_out = 4 * M * 64;
+    for (int k0 = 0; k0 * 96 < n_out; k0 += 4) {
+        float4 acc[4];
+        int r[4];
+        const float* col[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int idx = min(ctid + 96 * (k0 + q), n_out - 1);
+            r[q] = idx >> 6;
+            col[q] = pb + r[q] * ATT_D + (idx & 63) * 4;
+            acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll 2
+        for (int sp = 0; sp < nsp; sp++) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float4* src = reinterpret_cast<const float4*>(col[q] + (size_t)sp * PART_STRIDE);
+                const float4 x = SM ? *src : __ldcg(src);
+                const float w = s_w[sp * 16 + r[q]];
+                acc[q].x += w * x.x; acc[q].y += w * x.y; acc[q].z += w * x.z; acc[q].w += w * x.w;
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int idx = ctid + 96 * (k0 + q);
+            if (idx < n_out) {
+                const float inv = s_w[nsp * 16 + r[q]];
+                uint2 v;
+                v.x = pack_bf16x2(acc[q].x * inv, acc[q].y * inv);
+                v.y = pack_bf16x2(acc[q].z * inv, acc[q].w * inv);
+                *reinterpret_cast<uint2*>(out_pair + ((size_t)(r[q] >> 2) * ATT_H + (r[q] & 3)) * ATT_D + (idx & 63) * 4) = v;
+            }
+        }
+    }
+}
 
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV) {
@@ -39,23 +127,86 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
     __shared__ uint32_t tmem_slot;
     __shared__ int s_abort, s_last;
     __shared__ float s_w[(148 + 2) * 16];                            // merge weights: [partials of a pair][16 rows], then 1 / sum
+    __shared__ int s_cum[TC_MAX_PAIRS + 1];                   // the plan: tile prefix sums of the pairs,
+    __shared__ int s_base[TC_MAX_PAIRS + 1];                  //   first partial slot of every pair,
+    __shared__ int s_ctx[TC_MAX_PAIRS / ATT_KV];              //   context lengths
+    __shared__ int s_scan[TC_THREADS / 32];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int M = a.M, P = a.P;
-    const int* cum = meta_cum(a.meta);
-    const long long N = a.meta[0];
-    const int G = a.meta[1];                                         // working blocks = min(grid, tiles)
-    if ((int)blockIdx.x >= G) return;
-    long long lo = (long long)blockIdx.x * N / G;
-    const long long hi = (long long)(blockIdx.x + 1) * N / G;
-    if (lo >= hi) return;
     const uint32_t sbase = smem_addr(smem);
     if (sbase & 1023u) { if (tid == 0) atomicExch(a.status, 4); return; }
+
+    // ---- the plan, computed by every block for itself (a few hundred integer operations; a kernel of its own in front of this one
+    //      costs a launch and a dependent start per layer).  Same plan as gqa_decode_plan_kernel: the tiles of all pairs laid end to
+    //      end, every pair followed by `tail_tiles` tiles of weight without work, cut into G equal ranges. ----
+    const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.meta + 2);
+    for (int i = tid; i < a.B; i += TC_THREADS) s_ctx[i] = a.ctx_len[i];
+    __syncthreads();
+    const int* cum = s_cum;
+    const int* ctxv = s_ctx;
+    auto block_scan = [&](int local) -> int {                        // exclusive prefix of `local` over the block
+        int x = local;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int y = __shfl_up_sync(0xffffffffu, x, o); if (lane >= o) x += y; }
+        __syncthreads();
+        if (lane == 31) s_scan[warp] = x;
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; w++) before += s_scan[w];
+        return before + x - local;
+    };
+    const int chunk = (P + TC_THREADS - 1) / TC_THREADS, p0 = min(P, tid * chunk), p1 = min(P, p0 + chunk);
+    auto tiles_of = [&](int p) -> int {
+        const int ctx = s_ctx[p / ATT_KV];
+        if (ctx < 0 || (long long)ctx + M > (long long)a.max_pages * a.page_size) { atomicExch(a.status, 1); return 0; }
+        return (ctx + TK - 1) / TK + 1 + a.tail_tiles;
+    };
+    {
+        int local = 0;
+        for (int p = p0; p < p1; p++) local += tiles_of(p);
+        int run = block_scan(local);
+        for (int p = p0; p < p1; p++) { s_cum[p] = run; run += tiles_of(p); }
+        if (tid == TC_THREADS - 1) s_cum[P] = run;                   // (the last thread's chunk ends the range, or is empty: run = total)
+    }
+    __syncthreads();
+    const long long N = s_cum[P];
+    // with fewer tiles than blocks only the first N blocks work (one tile each): every working block then has a non-empty range
+    const int G = (int)min((long long)gridDim.x, max(N, 1ll));
+    auto first_block = [&](int p) -> int { return block_of_tile(s_cum[p], G, N); };
+    auto partials_of = [&](int p) -> int {                           // blocks that hold tiles with work of pair p (consecutive)
+        return s_cum[p + 1] > s_cum[p] ? block_of_tile(s_cum[p + 1] - 1 - a.tail_tiles, G, N) - first_block(p) + 1 : 0;
+    };
+    {
+        int local = 0;
+        for (int p = p0; p < p1; p++) local += partials_of(p);
+        int run = block_scan(local);
+        for (int p = p0; p < p1; p++) { s_base[p] = run; run += partials_of(p); }
+        if (tid == TC_THREADS - 1) s_base[P] = run;
+    }
+    __syncthreads();
+    if ((int)blockIdx.x >= G || N == 0) return;
+    long long lo = (long long)blockIdx.x * N / G;
+    const long long hi = (long long)(blockIdx.x + 1) * N / G;
+    // Arrival counters in the workspace: 64-bit words {tag, count}, valid only while the tag is the one of this call's epoch; the
+    // block that arrives last at the end of the kernel advances the epoch word, which invalidates every counter at once.  Nothing
+    // has to be zeroed between calls, and whatever an allocator left in the workspace reads as "no arrivals yet".  A block first
+    // `touch`es a counter it will arrive at (long before it does: if the word is stale, one compare-and-swap -- whoever wins --
+    // makes it {tag, 0}); the arrival itself is then a plain atomic add.
+    unsigned long long* counters = reinterpret_cast<unsigned long long*>(a.meta + 4);      // [0] blocks done, [1 + p] partials of pair p
+    auto tag_of = [&](int idx) -> uint32_t { return epoch * 0x9E3779B1u + (uint32_t)idx + 1u; };
+    auto touch = [&](int idx) {
+        const unsigned long long v = *reinterpret_cast<volatile unsigned long long*>(counters + idx);
+        if ((uint32_t)(v >> 32) != tag_of(idx)) atomicCAS(counters + idx, v, (unsigned long long)tag_of(idx) << 32);
+    };
+    auto arrive = [&](int idx) -> uint32_t { return (uint32_t)atomicAdd(counters + idx, 1ull); };      // how many arrived before
+    if (tid == 0) touch(0);
     auto bar = [&](int i) -> uint32_t { return smem_addr(&bars[i]); };
     if (tid == 0) {
         for (int i = 0; i < 3; i++) { mbar_init(bar(TB_FULL0 + i), 1); mbar_init(bar(TB_EMPTY0 + i), 1); }
         for (int i = 0; i < 2; i++) { mbar_init(bar(TB_SDONE0 + i), 1); mbar_init(bar(TB_SFREE0 + i), 1); mbar_init(bar(TB_PREADY0 + i), 1); mbar_init(bar(TB_PFREE0 + i), 1); }
         mbar_init(bar(TB_ODONE), 1);
+        mbar_init(bar(TB_MERGE), 1);
         s_abort = 0;
         fence_barrier_init();
         tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -81,75 +232,58 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
     };
 
     const uint32_t sQ = sbase, sKV = sbase + TC_Q_BYTES;
-    uint32_t n0 = 0;                                                 // tiles this block has put through the ring before the current pair
-    uint32_t pairs_done = 0;
     int pair;                                                        // pair that owns tile lo: cum[pair] <= lo < cum[pair + 1]
     {
         int l = 0, r = P - 1;
         while (l < r) { const int m = (l + r + 1) >> 1; if (cum[m] <= lo) l = m; else r = m - 1; }
         pair = l;
     }
-    for (; lo < hi; pair++) {
-        if (cum[pair + 1] <= lo) continue;                           // pairs without tiles (rejected sequences)
-        const long long seg_end = min(hi, (long long)cum[pair + 1]);
-        const int ta = (int)(lo - cum[pair]), tbk = (int)(seg_end - cum[pair]);      // this block's tiles of the pair: [ta, tbk)
-        const int slot = meta_base(a.meta, P)[pair] + ((int)blockIdx.x - meta_first(a.meta, P)[pair]);
-        lo = seg_end;
-        const int b = pair / ATT_KV, kvh = pair % ATT_KV;
-        const int ctx = a.ctx_len[b];
-        const int all_ctx_tiles = (ctx + TK - 1) / TK;               // tile index all_ctx_tiles holds the rows of this call
-        const int ctx_tiles = max(0, min(tbk, all_ctx_tiles) - ta);
-        const int ntiles = tbk - ta;
-        const int k_begin = ta * TK;
-        const int k_end = min(ctx, (ta + ctx_tiles) * TK);
-        const int* table = a.block_table + (size_t)b * a.max_pages;
+    // the three consumer warps synchronise among themselves; the producer runs ahead on its own, across pair boundaries
+    auto csync = [&]() { asm volatile("bar.sync 1, 96;" ::: "memory"); };
+    const int ctid = warp < 2 ? tid : tid - 32;                      // 0..95 over warps 0, 1, 3
 
-        // ---- prologue: Q rows into the operand slabs (row r = j*4 + hq <-> q[(b*M + j), kvh*4 + hq, :]; rows >= 4M zero) and, in the
-        //      block that owns the pair's first tile, the new rows into the cache (readers take them from the inputs) ----
-        if (warp == 3) {
-            for (int i = lane; i < 16 * 32; i += 32) {
-                const int r = i >> 5, c = i & 31, j = r >> 2, hq = r & 3;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (j < M) v = reinterpret_cast<const uint4*>(a.q + (((size_t)b * M + j) * ATT_H + kvh * ATT_GQA + hq) * ATT_D)[c];
-                unsigned char* dst = smem + (c >> 3) * 4096 + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-                *reinterpret_cast<uint4*>(dst) = v;
-                *reinterpret_cast<uint4*>(dst + 2048) = v;             // rows 16..31 repeat rows 0..15 (r + 16 has the same r & 7)
-            }
-            fence_proxy_async_smem();
-            if (ta == 0) {
-                for (int i = lane; i < M * 64; i += 32) {
-                    const int jj = i >> 6, c = i & 31, isv = (i >> 5) & 1;
-                    const int pos = ctx + jj;
-                    const int page = table[pos / a.page_size];
-                    if (page < 0 || page >= a.n_pages) { atomicExch(a.status, 1); continue; }
-                    const __nv_bfloat16* src = (isv ? a.v_new : a.k_new) + (((size_t)b * M + jj) * ATT_KV + kvh) * ATT_D;
-                    __nv_bfloat16* dst = (isv ? a.v_pages : a.k_pages) + (((size_t)page * ATT_KV + kvh) * a.page_size + pos % a.page_size) * ATT_D;
-                    reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+    if (warp == 2) {
+        // ================= producer: keep the ring full with every tile of this block's range, pair after pair =================
+        uint32_t n = 0;
+        long long plo = lo;
+        // the cache is read once per call: its lines are the first to leave L2, so that the plan, the page table, the partials and
+        // the code stay there while hundreds of megabytes stream through
+        uint64_t stream_policy;
+        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(stream_policy));
+        for (int pp = pair; plo < hi && !aborted(); pp++) {
+            if (cum[pp + 1] <= plo) continue;
+            const long long seg_end = min(hi, (long long)cum[pp + 1]);
+            const int ta = (int)(plo - cum[pp]), tbk = (int)(seg_end - cum[pp]);
+            plo = seg_end;
+            const int b = pp / ATT_KV, kvh = pp % ATT_KV;
+            const int ctx = ctxv[b];
+            const int all_ctx = (ctx + TK - 1) / TK;
+            const int ctx_tiles = max(0, min(tbk, all_ctx) - ta);
+            const int ntiles = max(0, min(tbk, all_ctx + 1) - ta);         // tiles past all_ctx are the plan's weight of the epilogue: no work
+            const int* table = a.block_table + (size_t)b * a.max_pages;
+            bool okp = true;
+            int my_page = 0;
+            for (int t = 0; t < ntiles && okp; t++, n++) {
+                if ((t & 31) == 0) {                                     // page numbers of the next 32 tiles, one lane each
+                    const int e = (int)(((long long)(ta + t + lane) * TK) / a.page_size);
+                    my_page = (t + lane < ctx_tiles && e < a.max_pages) ? table[e] : 0;
                 }
-            }
-        }
-        __syncthreads();
-
-        if (warp == 2) {
-            // ================= producer: keep the ring full with the tiles [ta, tbk) of this pair =================
-            for (int t = 0; t < ntiles && !aborted(); t++) {
-                const uint32_t n = n0 + t;
+                int page = __shfl_sync(0xffffffffu, my_page, t & 31);
                 const int stage = n % ATT_STAGES;
-                if (n >= (uint32_t)ATT_STAGES && !wait(TB_EMPTY0 + stage, (n / ATT_STAGES) - 1)) break;
+                if (n >= (uint32_t)ATT_STAGES && !wait(TB_EMPTY0 + stage, (n / ATT_STAGES) - 1)) { okp = false; break; }
                 const uint32_t dK = sKV + stage * 2 * TILE_BYTES, dV = dK + TILE_BYTES;
                 if (t < ctx_tiles) {
                     if (lane == 0) {
-                        const int key = k_begin + t * TK;
-                        int page = table[key / a.page_size];
+                        const int key = (ta + t) * TK;
                         if (page < 0 || page >= a.n_pages) { atomicExch(a.status, 1); page = 0; }      // reported; page 0 is read in its place
                         const int row = key % a.page_size;
                         mbar_expect_tx(bar(TB_FULL0 + stage), 2 * TILE_BYTES);
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
-                            asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-                                         ::"r"(dK + j * 8192), "l"(&tmK), "r"(bar(TB_FULL0 + stage)), "r"(64 * j), "r"(row), "r"(kvh), "r"(page) : "memory");
-                            asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-                                         ::"r"(dV + j * 8192), "l"(&tmV), "r"(bar(TB_FULL0 + stage)), "r"(64 * j), "r"(row), "r"(kvh), "r"(page) : "memory");
+                            asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+                                         ::"r"(dK + j * 8192), "l"(&tmK), "r"(bar(TB_FULL0 + stage)), "r"(64 * j), "r"(row), "r"(kvh), "r"(page), "l"(stream_policy) : "memory");
+                            asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+                                         ::"r"(dV + j * 8192), "l"(&tmV), "r"(bar(TB_FULL0 + stage)), "r"(64 * j), "r"(row), "r"(kvh), "r"(page), "l"(stream_policy) : "memory");
                         }
                     }
                 } else {
@@ -170,7 +304,87 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
                     if (lane == 0) mbar_arrive(bar(TB_FULL0 + stage));
                 }
             }
-        } else if (warp == 1) {
+            if (!okp) break;
+        }
+    } else {
+    uint32_t n0 = 0;                                                 // tiles this block has put through the ring before the current pair
+    uint32_t pairs_done = 0, merges_done = 0;                       // pairs seen; merges that went through the ring
+    // work of this block in pair pr, from tile l on: the tiles past the pair's last real one are the plan's weight of its epilogue
+    auto seg_tiles = [&](int pr, long long l) -> int {
+        const int ta = (int)(l - cum[pr]), tbk = (int)(min(hi, (long long)cum[pr + 1]) - cum[pr]);
+        return max(0, min(tbk, (ctxv[pr / ATT_KV] + TK - 1) / TK + 1) - ta);
+    };
+    auto next_seg = [&](int pr, long long l, int& npair, int& nta) -> bool {      // first segment with work after (pr, l); l = its start
+        for (pr++; l < hi; pr++) {
+            if (cum[pr + 1] <= l) continue;
+            if (seg_tiles(pr, l) > 0) { npair = pr; nta = (int)(l - cum[pr]); return true; }
+            l = min(hi, (long long)cum[pr + 1]);
+        }
+        return false;
+    };
+    // warp 3 keeps the Q rows of the next pair in registers: fetched while the current pair streams (a load issued then takes
+    // microseconds, the memory system being saturated by the copies), written to the operand slabs when the tensor pipe is done
+    uint4 qreg[16];
+    bool q_have = false;
+    auto q_fetch = [&](int pr) {
+        const int b = pr / ATT_KV, kvh = pr % ATT_KV;
+#pragma unroll
+        for (int r = 0; r < 16; r++) {
+            const int j = r >> 2, hq = r & 3;
+            qreg[r] = make_uint4(0, 0, 0, 0);
+            if (j < M) qreg[r] = reinterpret_cast<const uint4*>(a.q + (((size_t)b * M + j) * ATT_H + kvh * ATT_GQA + hq) * ATT_D)[lane];
+        }
+    };
+    auto q_put = [&]() {                                             // row r = j*4 + hq; rows 16..31 repeat rows 0..15; rows >= 4M zero
+#pragma unroll
+        for (int r = 0; r < 16; r++) {
+            unsigned char* dst = smem + (lane >> 3) * 4096 + r * 128 + (((lane & 7) ^ (r & 7)) << 4);
+            *reinterpret_cast<uint4*>(dst) = qreg[r];
+            *reinterpret_cast<uint4*>(dst + 2048) = qreg[r];         // (r + 16 has the same r & 7)
+        }
+        fence_proxy_async_smem();
+    };
+    auto append = [&](int pr) {                                      // the rows of this call into the cache (readers take them from the inputs)
+        const int b = pr / ATT_KV, kvh = pr % ATT_KV;
+        const int ctx = ctxv[b];
+        const int* table = a.block_table + (size_t)b * a.max_pages;
+        for (int i = lane; i < M * 64; i += 32) {
+            const int jj = i >> 6, c = i & 31, isv = (i >> 5) & 1;
+            const int pos = ctx + jj;
+            const int page = table[pos / a.page_size];
+            if (page < 0 || page >= a.n_pages) { atomicExch(a.status, 1); continue; }
+            const __nv_bfloat16* src = (isv ? a.v_new : a.k_new) + (((size_t)b * M + jj) * ATT_KV + kvh) * ATT_D;
+            __nv_bfloat16* dst = (isv ? a.v_pages : a.k_pages) + (((size_t)page * ATT_KV + kvh) * a.page_size + pos % a.page_size) * ATT_D;
+            reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+        }
+    };
+    for (; lo < hi; pair++) {
+        if (cum[pair + 1] <= lo) continue;                           // pairs without tiles (rejected sequences)
+        if (seg_tiles(pair, lo) == 0) { lo = min(hi, (long long)cum[pair + 1]); continue; }      // only weight tiles of this pair: no partial either
+        const long long seg_end = min(hi, (long long)cum[pair + 1]);
+        const int ta = (int)(lo - cum[pair]), tbk = (int)(seg_end - cum[pair]);      // this block's tiles of the pair: [ta, tbk)
+        const int slot = s_base[pair] + ((int)blockIdx.x - first_block(pair));
+        if (ctid == 0) touch(1 + pair);
+        int npair = 0, nta = 0;
+        const bool has_next = next_seg(pair, seg_end, npair, nta);  // (the same answer in every thread)
+        lo = seg_end;
+        const int b = pair / ATT_KV, kvh = pair % ATT_KV;
+        const int ctx = ctxv[b];
+        const int all_ctx_tiles = (ctx + TK - 1) / TK;               // tile index all_ctx_tiles holds the rows of this call
+        const int ctx_tiles = max(0, min(tbk, all_ctx_tiles) - ta);
+        const int ntiles = max(0, min(tbk, all_ctx_tiles + 1) - ta);   // tiles past all_ctx_tiles are the plan's weight of the epilogue: no work
+        const int k_begin = ta * TK;
+        const int k_end = min(ctx, (ta + ctx_tiles) * TK);
+
+        // ---- prologue: Q rows into the operand slabs and, in the block that owns the pair's first tile, the new rows into the cache ----
+        if (warp == 3) {
+            if (!q_have) { q_fetch(pair); if (ta == 0) append(pair); }
+            q_put();
+        }
+        csync();
+        if (pairs_done == 0) GDN_BSTAMP(6);
+
+        if (warp == 1) {
             // ================= MMA issuer =================
             if (lane == 0) {
                 constexpr uint32_t I_QK = idesc_bf16(128, 64, 0, 0);
@@ -201,6 +415,7 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
                     ok = wait(TB_FULL0 + stage, n / ATT_STAGES) && (n < 2 || wait(TB_SFREE0 + buf, (n >> 1) - 1));
                     if (!ok) break;
                     tc_fence_after_sync();
+                    if (n == 0) GDN_BSTAMP_ANY(10);
                     GDN_TSTAMP(n * 8 + 0);
                     const uint32_t klo = smem_desc_lo(sKV + stage * 2 * TILE_BYTES, 16), qlo = smem_desc_lo(sQ, 16);
 #pragma unroll
@@ -318,9 +533,11 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
                 GDN_TSTAMP(n * 8 + 7);
             }
             // ---- epilogue: O / l (the whole pair was this block's) or a partial (max, sum, O) for the merge ----
+            if (pairs_done == 0 && lane == 0) GDN_BSTAMP_ANY(7);
             if (ok) ok = wait(TB_ODONE, pairs_done);
             tc_fence_after_sync();
-            const int nsp = meta_base(a.meta, P)[pair + 1] - meta_base(a.meta, P)[pair];
+            if (pairs_done == 0 && lane == 0) GDN_BSTAMP_ANY(8);
+            const int nsp = s_base[pair + 1] - s_base[pair];
             float* part = a.part + (size_t)slot * PART_STRIDE;
             l_run += __shfl_xor_sync(0xffffffffu, l_run, 16);
             const bool row_ok = ok && lane < 4 * M;                  // lanes 0..15 write the rows
@@ -353,84 +570,66 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
                 }
             }
             if (row_ok && nsp > 1) { part[16 * ATT_D + 2 * lane] = m_run; part[16 * ATT_D + 2 * lane + 1] = l_run; }
+            if (pairs_done == 0 && lane == 0) GDN_BSTAMP_ANY(9);
             tc_fence_before_sync();
+        } else if (warp == 3) {
+            // ================= look-ahead: the next pair's Q rows (and its append) while this one streams =================
+            q_have = has_next;
+            if (has_next) { q_fetch(npair); if (nta == 0) append(npair); }
         }
         n0 += ntiles;
         pairs_done++;
         GDN_BSTAMP(1 + 2 * (pairs_done > 1));
 
         // ---- merge: the block that writes the last partial of a pair combines them (the counters were zeroed by this call's plan kernel) ----
-        const int* pbase = meta_base(a.meta, P);
+        const int* pbase = s_base;
         const int nsp = pbase[pair + 1] - pbase[pair];
         __threadfence();
-        __syncthreads();
+        csync();
         if (nsp > 1) {
-            if (tid == 0) s_last = (!aborted() && atomicAdd(meta_count(a.meta, P) + pair, 1) == nsp - 1) ? 1 : 0;
-            __syncthreads();
+            if (ctid == 0) s_last = (!aborted() && arrive(1 + pair) == (uint32_t)(nsp - 1)) ? 1 : 0;
+            csync();
+            GDN_BSTAMP(13);
             if (s_last && nsp <= 148) {
                 __threadfence();
                 const float* pb = a.part + (size_t)pbase[pair] * PART_STRIDE;
-                for (int i = tid; i < nsp * 16; i += TC_THREADS) s_w[i] = __ldcg(pb + (size_t)(i >> 4) * PART_STRIDE + 16 * ATT_D + 2 * (i & 15));
-                __syncthreads();
-                if (tid < 16) {
-                    float ms = -INFINITY, lsum = 0.f;
-                    for (int sp = 0; sp < nsp; sp++) ms = fmaxf(ms, s_w[sp * 16 + tid]);
-                    for (int sp = 0; sp < nsp; sp++) {
-                        const float m = s_w[sp * 16 + tid];
-                        const float w = (m == -INFINITY) ? 0.f : exp2f(m - ms);
-                        lsum += w * __ldcg(pb + (size_t)sp * PART_STRIDE + 16 * ATT_D + 2 * tid + 1);
-                        s_w[sp * 16 + tid] = w;
-                    }
-                    s_w[nsp * 16 + tid] = lsum == 0.f ? 1.f : 1.f / lsum;
-                }
-                __syncthreads();
+                float* s_l = reinterpret_cast<float*>(smem);         // the partials' sums: the Q operand is idle between pairs
                 __nv_bfloat16* out_pair = a.out + ((size_t)b * M * ATT_H + kvh * ATT_GQA) * ATT_D;
-                // thread = (row pair, 16 dims): every partial contributes 8 independent 16-byte loads, and the loop over partials is
-                // unrolled, so a few dozen loads are in flight per thread (the partials sit in L2; the merge is latency-bound)
-                const int rp = tid >> 4, d0 = (tid & 15) * 16;
-                float acc[2][16];
-#pragma unroll
-                for (int q = 0; q < 2; q++)
-#pragma unroll
-                    for (int i = 0; i < 16; i++) acc[q][i] = 0.f;
-#pragma unroll 4
-                for (int sp = 0; sp < nsp; sp++) {
-#pragma unroll
-                    for (int q = 0; q < 2; q++) {
-                        const int r = 2 * rp + q;
-                        const float w = s_w[sp * 16 + r];
-                        const float4* pp = reinterpret_cast<const float4*>(pb + (size_t)sp * PART_STRIDE + r * ATT_D + d0);
-#pragma unroll
-                        for (int v4 = 0; v4 < 4; v4++) {
-                            const float4 x = __ldcg(pp + v4);
-                            acc[q][4 * v4] += w * x.x; acc[q][4 * v4 + 1] += w * x.y; acc[q][4 * v4 + 2] += w * x.z; acc[q][4 * v4 + 3] += w * x.w;
-                        }
+                if (!has_next && nsp <= TC_RING_PARTIALS) {
+                    // the block's last pair: the ring is idle, so the partials come in as bulk copies, all in flight at once (read
+                    // through registers they cost several dependent round trips to L2)
+                    unsigned char* ring = smem + TC_Q_BYTES;
+                    if (ctid == 0) {
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                        mbar_expect_tx(bar(TB_MERGE), (uint32_t)nsp * PART_STRIDE * 4);
+                        for (int sp = 0; sp < nsp; sp++)
+                            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                         ::"r"(smem_addr(ring + (size_t)sp * PART_STRIDE * 4)), "l"(pb + (size_t)sp * PART_STRIDE), "r"(PART_STRIDE * 4), "r"(bar(TB_MERGE)) : "memory");
                     }
-                }
-#pragma unroll
-                for (int q = 0; q < 2; q++) {
-                    const int r = 2 * rp + q;
-                    if (r < 4 * M) {
-                        const float inv = s_w[nsp * 16 + r];
-                        __nv_bfloat16* dst = out_pair + ((size_t)(r >> 2) * ATT_H + (r & 3)) * ATT_D + d0;
-                        uint4 v0, v1;
-                        v0.x = pack_bf16x2(acc[q][0] * inv, acc[q][1] * inv); v0.y = pack_bf16x2(acc[q][2] * inv, acc[q][3] * inv);
-                        v0.z = pack_bf16x2(acc[q][4] * inv, acc[q][5] * inv); v0.w = pack_bf16x2(acc[q][6] * inv, acc[q][7] * inv);
-                        v1.x = pack_bf16x2(acc[q][8] * inv, acc[q][9] * inv); v1.y = pack_bf16x2(acc[q][10] * inv, acc[q][11] * inv);
-                        v1.z = pack_bf16x2(acc[q][12] * inv, acc[q][13] * inv); v1.w = pack_bf16x2(acc[q][14] * inv, acc[q][15] * inv);
-                        reinterpret_cast<uint4*>(dst)[0] = v0;
-                        reinterpret_cast<uint4*>(dst)[1] = v1;
-                    }
+                    const bool got = wait(TB_MERGE, merges_done);
+                    GDN_BSTAMP(14);
+                    if (got) tc_merge_pair<true>(reinterpret_cast<const float*>(ring), nsp, s_w, s_l, out_pair, M, ctid);
+                    else { csync(); csync(); csync(); csync(); }     // (keeps the barrier count of the merge)
+                    merges_done++;
+                } else {
+                    tc_merge_pair<false>(pb, nsp, s_w, s_l, out_pair, M, ctid);
                 }
             }
-            __syncthreads();                                         // s_w and s_last are reused by the block's next pair
+            csync();                                         // s_w and s_last are reused by the block's next pair
         }
         GDN_BSTAMP(2 + 2 * (pairs_done > 1));
     }
+    GDN_BVAL(11, n0); GDN_BVAL(12, pairs_done);
+    }   // consumer warps
     tc_fence_before_sync();
     __syncthreads();
     GDN_BSTAMP(5);
     if (warp == 1) tmem_dealloc(tb, 512);
+    // the last block to get here -- blocks that gave up on a wait come here too -- starts the next call's epoch
+    if (tid == 0) {
+        __threadfence();
+        if (arrive(0) == (uint32_t)(G - 1)) { *reinterpret_cast<volatile uint32_t*>(a.meta + 2) = epoch + 1u; __threadfence(); }
+    }
 }
 
 int launch_gqa_decode_tc(const AttnArgs& a, const CUtensorMap& tk, const CUtensorMap& tv, cudaStream_t stream) {

@@ -53,6 +53,7 @@ struct AttnArgs {
     int* status;
     int B, M, page_size, max_pages, n_pages;
     int P, G;                                   // pairs (= 2 B) and persistent blocks; filled in by the launcher
+    int tail_tiles;                             // plan weight of a pair's epilogue, in tiles (filled in by the launcher)
 };
 
 size_t gqa_workspace_bytes(int B, int max_ctx);

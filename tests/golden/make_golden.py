@@ -38,7 +38,9 @@ def warm_state(scale):
 
 
 def main():
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path of a checkout of the reference project>")
+    ref_root = Path(sys.argv[1])
     rec64 = reference_rec64(ref_root)
     out = {}
     for name, T, seed, state_scale in (("zero_state", 24, 0, 0.0), ("warm_state", 17, 1, 0.02)):
