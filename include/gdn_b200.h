@@ -122,6 +122,17 @@ GDN_API int gdn_phase_b(const void* q, const void* k, const void* v, const void*
                 const float* init_state, const int* init_idx, void* y, float* final_state, int n_seq, long long total_T, int H, int head_lo,
                 int head_hi, void* stream);
 
+/* Phase B with the gated RMSNorm of the layer fused into its y store: y <- bf16(silu(z) * (gate_w * (y * rsqrt(mean(y^2) + 1e-6))))
+ * per (token, head) row, computed on the bf16-rounded y exactly as gdn_gated_norm does (same bits as gdn_phase_b followed by
+ * gdn_gated_norm), so the y tensor never makes the round trip through memory between the two.
+ * Replaces: phase_b followed by gated_norm, qwen35/prefill.py:253-254 (gated_norm :137-157,241-244).
+ *   gate_z bf16: the z slice of the projection rows, element (t, h, c) at gate_z[t * gate_stride + h * 128 + c]
+ *   (for in_proj rows: proj + 6144, gate_stride = the row stride); 16-byte aligned rows.  gate_w fp32 [128].
+ *   gate_z == gate_w == NULL: plain gdn_phase_b. */
+GDN_API int gdn_phase_b_gated(const void* q, const void* k, const void* v, const void* records, size_t records_bytes, const int* cu_seqlens,
+                      const float* init_state, const int* init_idx, const void* gate_z, long long gate_stride, const float* gate_w, void* y,
+                      float* final_state, int n_seq, long long total_T, int H, int head_lo, int head_hi, void* stream);
+
 /* Decode / speculative verify, solo flavour: M chained tokens, functional snapshot outputs.
  * Replaces: deltanet, qwen35/kernels.py:555-567 (kernel :461-552).
  *   proj bf16 [M, row_stride>=8224];  conv_snap bf16 [n_snap,3,6144];  conv_w bf16 [6144*4];  ssm_snap fp32 [n_snap,16,128,128]

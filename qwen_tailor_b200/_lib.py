@@ -33,6 +33,7 @@ SIGNATURES = {
     "gdn_phase_a": (I, [P, P, P, P, P, SZ, I, LL, I, I, I, P]),
     "gdn_prep_a": (I, [P, LL, P, P, P, P, P, P, P, P, P, SZ, I, LL, I, I, P]),
     "gdn_phase_b": (I, [P, P, P, P, SZ, P, P, P, P, P, I, LL, I, I, I, P]),
+    "gdn_phase_b_gated": (I, [P, P, P, P, SZ, P, P, P, P, LL, P, P, P, I, LL, I, I, I, P]),
     "gdn_deltanet": (I, [P, LL, P, P, P, P, P, P, I, P, P, P, I, P]),
     "gdn_deltanet_b": (I, [P, LL, P, P, P, P, P, P, P, I, P, I, P]),
     "gdn_deltanet_bm": (I, [P, LL, P, P, P, P, P, P, P, P, I, P, I, I, P]),

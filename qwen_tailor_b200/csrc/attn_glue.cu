@@ -127,11 +127,13 @@ __global__ void gdn_gated_norm_kernel(const __nv_bfloat16* y, const __nv_bfloat1
     float yy[4], zz[4];
     unpack_bf16x4(*reinterpret_cast<const uint2*>(y + (size_t)t * (HV * DV) + hv * DV + c0), yy);
     unpack_bf16x4(*reinterpret_cast<const uint2*>(proj + (size_t)t * row_stride + CD + hv * DV + c0), zz);
-    const float ss = warp_sum((yy[0] * yy[0] + yy[1] * yy[1]) + (yy[2] * yy[2] + yy[3] * yy[3]));
-    const float inv = 1.0f / sqrtf(ss / 128.f + 1e-6f);
+    float ss = gnorm_sq4(yy);
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);      // neighbouring groups first (see gnorm_sq4)
+    const float inv = gnorm_inv(ss);
     float r[4];
 #pragma unroll
-    for (int i = 0; i < 4; i++) r[i] = zz[i] / (1.f + expf(-zz[i])) * (gw[c0 + i] * (yy[i] * inv));
+    for (int i = 0; i < 4; i++) r[i] = gnorm_elem(zz[i], yy[i], inv, gw[c0 + i]);
     uint2 pk;
     pk.x = pack_bf16x2(r[0], r[1]);
     pk.y = pack_bf16x2(r[2], r[3]);

@@ -151,7 +151,17 @@ int gdn_prep_a(const void* proj, long long row_stride, const void* conv_state, c
 int gdn_phase_b(const void* q, const void* k, const void* v, const void* records, size_t records_bytes, const int* cu_seqlens,
                 const float* init_state, const int* init_idx, void* y, float* final_state, int n_seq, long long total_T, int H, int head_lo,
                 int head_hi, void* stream) {
+    return gdn_phase_b_gated(q, k, v, records, records_bytes, cu_seqlens, init_state, init_idx, nullptr, 0, nullptr, y, final_state, n_seq, total_T, H,
+                             head_lo, head_hi, stream);
+}
+
+int gdn_phase_b_gated(const void* q, const void* k, const void* v, const void* records, size_t records_bytes, const int* cu_seqlens,
+                      const float* init_state, const int* init_idx, const void* gate_z, long long gate_stride, const float* gate_w, void* y,
+                      float* final_state, int n_seq, long long total_T, int H, int head_lo, int head_hi, void* stream) {
     REQUIRE(q && k && v && y && final_state, GDN_E_NULL, "gdn_phase_b: null pointer");
+    REQUIRE((gate_z == nullptr) == (gate_w == nullptr), GDN_E_NULL, "gdn_phase_b_gated: gate_z and gate_w go together");
+    REQUIRE(!gate_w || (gate_stride >= (long long)H * 128 && gate_stride % 8 == 0 && aligned16(gate_z) && aligned16(gate_w)), GDN_E_ALIGN,
+            "gdn_phase_b_gated: gate rows must be 16-byte aligned (stride %lld elements)", gate_stride);
     int rc = prefill_common("gdn_phase_b", cu_seqlens, records, records_bytes, n_seq, total_T, H, head_lo, head_hi);
     if (rc) return rc;
     REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(init_state) && aligned16(final_state), GDN_E_ALIGN,
@@ -162,6 +172,7 @@ int gdn_phase_b(const void* q, const void* k, const void* v, const void* records
     a.cu_seqlens = cu_seqlens; a.init_state = init_state; a.init_idx = init_idx;
     a.y = static_cast<__nv_bfloat16*>(y); a.final_state = final_state;
     a.n_seq = n_seq; a.H = H; a.head_lo = head_lo; a.n_heads = head_hi - head_lo;
+    a.gate_z = static_cast<const __nv_bfloat16*>(gate_z); a.gate_stride = gate_stride; a.gate_w = gate_w;
     a.status = status_ptr();
     REQUIRE(a.status, GDN_E_LAUNCH, "gdn_phase_b: no CUDA device");
     a.total_T = total_T == 0 ? 1 : total_T;     // a tensor map needs a non-empty extent; empty sequences never issue a copy

@@ -66,6 +66,17 @@ __device__ __forceinline__ long long gdn_globaltimer() { long long t; asm volati
 #define GDN_BSTAMP_ANY(k) do { } while (0)
 #endif
 
+// The gated RMSNorm of the GDN output (qwen35/prefill.py:137-157): out = silu(z) * (w * (y * inv)), inv = rsqrt(mean(y^2) + 1e-6).
+// One definition for the stand-alone kernel and for the fused y store of the prefill kernel, so that both give the same bits:
+// the 128 squares of a row are summed as (y0^2 + y1^2) + (y2^2 + y3^2) per group of four, then pairwise over neighbouring groups
+// (group g with g ^ 1, then ^ 2, ^ 4, ^ 8, ^ 16).  exp, the division and rsqrt use the fast hardware approximations (a few fp32 ulp,
+// far below the bf16 rounding of the result).
+__device__ __forceinline__ float gnorm_sq4(const float* y) { return (y[0] * y[0] + y[1] * y[1]) + (y[2] * y[2] + y[3] * y[3]); }
+__device__ __forceinline__ float gnorm_inv(float ss) { return rsqrtf(fmaf(ss, 1.f / 128.f, 1e-6f)); }
+__device__ __forceinline__ float gnorm_elem(float z, float y, float inv, float w) {
+    return __fmul_rn(__fdividef(z, 1.f + __expf(-z)), __fmul_rn(w, __fmul_rn(y, inv)));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

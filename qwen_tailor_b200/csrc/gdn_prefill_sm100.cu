@@ -61,7 +61,8 @@ constexpr int SM_A_LO = SM_A_HI + 8192;
 constexpr int SM_DP_HI = SM_A_LO + 8192;             // Dp^T hi / lo: [128][64] bf16, K-major, 16 KiB each
 constexpr int SM_DP_LO = SM_DP_HI + 16384;
 constexpr int SM_Y = SM_DP_LO + 16384;               // y tile of the chunk, [64 tokens][128 value columns] bf16, staged for row-wise stores (16 KiB)
-constexpr int SM_TOTAL = SM_Y + 16384;
+constexpr int SM_Z = SM_Y + 16384;                    // gate rows of the chunk (fused gated norm), same shape as the y tile (16 KiB)
+constexpr int SM_TOTAL = SM_Z + 16384;
 static_assert(ST_DEC + 256 <= SM_STAGE && ST_DEC + 256 - ST_REC == PA_REC_BYTES, "record layout");
 // ---- tensor memory map (columns) ----
 constexpr uint32_t TM_S = 0;                         // fp32 state, pre-scaled by the coming chunk's gamma_C   [128 cols]
@@ -88,6 +89,8 @@ __device__ __forceinline__ void bulk_load_rec(uint32_t dst, const void* src, uin
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
+// GATED: the layer's gated RMSNorm is applied in the y store (PrefillArgs::gate_*).
+template <bool GATED>
 __global__ void __launch_bounds__(PB_THREADS, 1)
 gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const PrefillArgs a) {
@@ -330,6 +333,17 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const uint32_t par = (uint32_t)c;
             const int t0 = t_begin + c * CH;
             const int nrows = min(CH, t_end - t0);
+            if (GATED) {                                          // fused gated norm: the chunk's gate rows travel to shared memory meanwhile
+                const int ot = tid - N_CHAIN_WARPS * 32;
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    const int i = (ot >> 4) + 8 * k;
+                    if (i < nrows)
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sbase + SM_Z + (i * DV + (ot & 15) * 8) * 2),
+                                     "l"(a.gate_z + (size_t)(t0 + i) * a.gate_stride + h * DV + (ot & 15) * 8) : "memory");
+                }
+                asm volatile("cp.async.commit_group;" ::: "memory");
+            }
             if (!out_wait((c & 1) ? B_FULL1 : B_FULL0, (uint32_t)(c >> 1))) break;      // Lc and gamma of the chunk have landed
             // ---- A = lower_incl(exp(Lc_i - Lc_j) Q K^T) as bf16 hi/lo K-major rows (the previous chunk's D^T A^T has completed) ----
             if (!out_wait(B_GDONE, par)) break;
@@ -401,6 +415,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     }
                 }
                 warp_arrive((c & 1) ? B_EMPTY1 : B_EMPTY0);          // gamma was this warp's last read of the stage
+                const int ot = tid - N_CHAIN_WARPS * 32;             // 0..127: row (ot >> 4) + 8 k, 16-byte word ot & 15 of the y tile
                 // transpose through shared memory: a lane owns one value column of all 64 tokens, the rows of y want 256 contiguous bytes
                 __nv_bfloat16* ys = reinterpret_cast<__nv_bfloat16*>(smem + SM_Y);
                 unsigned short* ysu = reinterpret_cast<unsigned short*>(ys);
@@ -413,13 +428,58 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     ysu[(32 + ii) * DV + r] = (unsigned short)pb;
                     ysu[(33 + ii) * DV + r] = (unsigned short)(pb >> 16);
                 }
+                if (GATED) asm volatile("cp.async.wait_group 0;" ::: "memory");      // this thread's part of the gate rows has landed
                 asm volatile("bar.sync 1, 128;" ::: "memory");       // the four output warps
-                const int ot = tid - N_CHAIN_WARPS * 32;             // 0..127
+                if (!GATED) {
 #pragma unroll
-                for (int k = 0; k < 8; k++) {
-                    const int p = ot + 128 * k, i = p >> 4, c16 = p & 15;
-                    if (i < nrows)
-                        *reinterpret_cast<uint4*>(a.y + ((size_t)(t0 + i) * a.H + h) * DV + c16 * 8) = *reinterpret_cast<const uint4*>(ys + i * DV + c16 * 8);
+                    for (int k = 0; k < 8; k++) {
+                        const int p = ot + 128 * k, i = p >> 4, c16 = p & 15;
+                        if (i < nrows)
+                            *reinterpret_cast<uint4*>(a.y + ((size_t)(t0 + i) * a.H + h) * DV + c16 * 8) = *reinterpret_cast<const uint4*>(ys + i * DV + c16 * 8);
+                    }
+                } else {
+                    // gated RMSNorm on the bf16 y rows (the stand-alone kernel's arithmetic, gnorm_* in gdn_common.cuh): sixteen
+                    // threads share a row, each with eight of its values = two of that kernel's groups of four
+                    const int c16 = ot & 15;
+                    // pass 1: the eight rows' sums of squares, their shuffle chains side by side
+                    float inv[8];
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        const uint4 yr = *reinterpret_cast<const uint4*>(ys + ((ot >> 4) + 8 * k) * DV + c16 * 8);
+                        float yy[8];
+                        unpack_bf16x4(make_uint2(yr.x, yr.y), yy);
+                        unpack_bf16x4(make_uint2(yr.z, yr.w), yy + 4);
+                        inv[k] = gnorm_sq4(yy) + gnorm_sq4(yy + 4);
+                    }
+#pragma unroll
+                    for (int o = 1; o < 16; o <<= 1) {
+#pragma unroll
+                        for (int k = 0; k < 8; k++) inv[k] += __shfl_xor_sync(0xffffffffu, inv[k], o);
+                    }
+#pragma unroll
+                    for (int k = 0; k < 8; k++) inv[k] = gnorm_inv(inv[k]);
+                    float gw8[8];                                    // the norm weights of this thread's eight columns
+                    *reinterpret_cast<float4*>(gw8) = __ldg(reinterpret_cast<const float4*>(a.gate_w + c16 * 8));
+                    *reinterpret_cast<float4*>(gw8 + 4) = __ldg(reinterpret_cast<const float4*>(a.gate_w + c16 * 8 + 4));
+                    // pass 2: the elements
+#pragma unroll
+                    for (int k = 0; k < 8; k++) {
+                        const int i = (ot >> 4) + 8 * k;
+                        const uint4 yr = *reinterpret_cast<const uint4*>(ys + i * DV + c16 * 8);
+                        float yy[8], zz[8];
+                        unpack_bf16x4(make_uint2(yr.x, yr.y), yy);
+                        unpack_bf16x4(make_uint2(yr.z, yr.w), yy + 4);
+                        const uint4 zr = *reinterpret_cast<const uint4*>(smem + SM_Z + (i * DV + c16 * 8) * 2);      // (written by this thread)
+                        unpack_bf16x4(make_uint2(zr.x, zr.y), zz);
+                        unpack_bf16x4(make_uint2(zr.z, zr.w), zz + 4);
+                        float r8[8];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) r8[e] = gnorm_elem(zz[e], yy[e], inv[k], gw8[e]);
+                        uint4 pk;
+                        pk.x = pack_bf16x2(r8[0], r8[1]); pk.y = pack_bf16x2(r8[2], r8[3]);
+                        pk.z = pack_bf16x2(r8[4], r8[5]); pk.w = pack_bf16x2(r8[6], r8[7]);
+                        if (i < nrows) *reinterpret_cast<uint4*>(a.y + ((size_t)(t0 + i) * a.H + h) * DV + c16 * 8) = pk;
+                    }
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");       // the tile may be overwritten by the next chunk
             }
@@ -602,11 +662,13 @@ int launch_phase_b(const void* q, const void* k, const void* v, const PrefillArg
     cudaGetDevice(&dev);
     const int smem = SM_TOTAL;
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(gdn_phase_b_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(gdn_phase_b_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+            cudaFuncSetAttribute(gdn_phase_b_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return check_launch("gdn_phase_b smem attribute");
         attr_set[dev] = true;
     }
-    gdn_phase_b_kernel<<<a.n_seq * a.n_heads, PB_THREADS, smem, stream>>>(tq, tk, tv, a);
+    if (a.gate_w) gdn_phase_b_kernel<true><<<a.n_seq * a.n_heads, PB_THREADS, smem, stream>>>(tq, tk, tv, a);
+    else gdn_phase_b_kernel<false><<<a.n_seq * a.n_heads, PB_THREADS, smem, stream>>>(tq, tk, tv, a);
     return check_launch("gdn_phase_b");
 }
 

@@ -94,6 +94,11 @@ struct PrefillArgs {
     int* status;
     int n_seq, H, head_lo, n_heads;
     long long total_T;
+    // optional gated RMSNorm fused into the y store (gate_w != nullptr): y <- silu(z) * rmsnorm(y) * gate_w with
+    // z = gate_z[t * gate_stride + h * 128 + c] (the z slice of the projection row of token t)
+    const __nv_bfloat16* gate_z;
+    long long gate_stride;
+    const float* gate_w;              // [128] fp32
 };
 int launch_phase_b(const void* q, const void* k, const void* v, const PrefillArgs& a, cudaStream_t stream);
 

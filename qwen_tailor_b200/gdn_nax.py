@@ -66,8 +66,25 @@ def phase_a_varlen(k, lg, beta, cu_seqlens, head_lo=0, head_hi=None, records=Non
     return records
 
 
-def phase_b_varlen(q, k, v, records, cu_seqlens, init_state=None, init_idx=None, head_lo=0, head_hi=None, y=None, final_state=None):
+def _gate_args(gate_proj, gate_w, total_T, H):
+    """(z pointer, row stride in elements, weight tensor) of the fused gated norm, or zeros when it is off."""
+    if gate_proj is None and gate_w is None:
+        return 0, 0, None
+    if gate_proj is None or gate_w is None:
+        raise ValueError("gdn_chunked: gate_proj and gate_w go together")
+    _lib.require_cuda(gate_proj, gate_w)
+    assert gate_proj.dtype == torch.bfloat16 and gate_proj.dim() == 2 and gate_proj.shape[0] == total_T and gate_proj.stride(1) == 1
+    assert H == 16 and gate_proj.shape[1] >= 8192, "the z slice is columns 6144:8192 of the in_proj rows"
+    gw = _f32(gate_w).reshape(-1)
+    assert gw.numel() == 128
+    return gate_proj.data_ptr() + 6144 * 2, gate_proj.stride(0), gw
+
+
+def phase_b_varlen(q, k, v, records, cu_seqlens, init_state=None, init_idx=None, head_lo=0, head_hi=None, y=None, final_state=None,
+                   gate_proj=None, gate_w=None):
     """Phase B over a packed batch: the serial chain of every (sequence, head) on the records of phase A.
+    With ``gate_proj`` (the in_proj rows [total_T, >= 8192] bf16) and ``gate_w`` ([128]) the layer's gated RMSNorm is applied in the
+    y store -- the same bits as ``prefill.gated_norm(y, gate_proj, gate_w)`` on the plain result (qwen35/prefill.py:253-254).
     Returns (y [total_T, H, 128] bf16, final_state [n_seq, H, 128, 128] fp32)."""
     _lib.require_cuda(q, k, v, records, cu_seqlens, init_state, init_idx)
     total_T, H = _check_qkv(q, k, v)
@@ -83,18 +100,22 @@ def phase_b_varlen(q, k, v, records, cu_seqlens, init_state=None, init_idx=None,
         y = torch.empty_like(q)
     if final_state is None:
         final_state = torch.empty((n_seq, H, 128, 128), dtype=torch.float32, device=q.device)
-    check(_lib.load().gdn_phase_b(ptr(q), ptr(k), ptr(v), ptr(records), records.numel(), ptr(cu_seqlens), ptr(init_state), ptr(init_idx), ptr(y),
-                                  ptr(final_state), n_seq, total_T, H, head_lo, head_hi, stream_ptr(q.device)), "gdn_phase_b")
+    gz, gstride, gw = _gate_args(gate_proj, gate_w, total_T, H)
+    check(_lib.load().gdn_phase_b_gated(ptr(q), ptr(k), ptr(v), ptr(records), records.numel(), ptr(cu_seqlens), ptr(init_state), ptr(init_idx),
+                                        gz, gstride, ptr(gw), ptr(y), ptr(final_state), n_seq, total_T, H, head_lo, head_hi, stream_ptr(q.device)),
+          "gdn_phase_b")
     return y, final_state
 
 
-def gdn_chunked_varlen(q, k, v, lg, beta, cu_seqlens, init_state=None, init_idx=None, head_lo=0, head_hi=None, y=None, final_state=None):
+def gdn_chunked_varlen(q, k, v, lg, beta, cu_seqlens, init_state=None, init_idx=None, head_lo=0, head_hi=None, y=None, final_state=None,
+                       gate_proj=None, gate_w=None):
     """Packed varlen chunked prefill (phase A, then phase B).
 
     q, k, v: [total_T, H, 128] bf16 (q, k normalised, q scaled by 128^-1/2); lg, beta: [total_T, H] fp32 (log-decay and beta);
     cu_seqlens: int32 [n_seq + 1] on the device; init_state: fp32 [*, H, 128, 128] or None (zero states); init_idx: int32 [n_seq]
     (row of init_state each sequence resumes from, negative = zero state) or None (row s for sequence s).
     Only heads [head_lo, head_hi) are computed (head-group sharding); the rest of y / final_state is left untouched.
+    ``gate_proj`` / ``gate_w``: fuse the gated RMSNorm into the y store (see ``phase_b_varlen``).
     Returns (y [total_T, H, 128] bf16, final_state [n_seq, H, 128, 128] fp32)."""
     _lib.require_cuda(q, k, v, lg, beta, cu_seqlens, init_state, init_idx)
     total_T, H = _check_qkv(q, k, v)
@@ -102,7 +123,7 @@ def gdn_chunked_varlen(q, k, v, lg, beta, cu_seqlens, init_state=None, init_idx=
     if not (0 <= head_lo <= head_hi_ <= H):
         raise ValueError(f"gdn_chunked: head range [{head_lo}, {head_hi_}) outside [0, {H})")
     rec = phase_a_varlen(k, lg, beta, cu_seqlens, head_lo, head_hi)
-    return phase_b_varlen(q, k, v, rec, cu_seqlens, init_state, init_idx, head_lo, head_hi, y, final_state)
+    return phase_b_varlen(q, k, v, rec, cu_seqlens, init_state, init_idx, head_lo, head_hi, y, final_state, gate_proj, gate_w)
 
 
 def prep_a(proj, conv_state, conv_w, A_log, dt_bias, relaxed=True):
@@ -136,10 +157,12 @@ def phase_a(q, k, proj, A_log, dt_bias, relaxed=True):
     return rec, torch.empty((0,), dtype=torch.float32, device=k.device), cu
 
 
-def phase_b(q, k, v, Tb, Am, gv, state, relaxed=True, flags=DEFAULT_FLAGS, tg=None):
+def phase_b(q, k, v, Tb, Am, gv, state, relaxed=True, flags=DEFAULT_FLAGS, tg=None, gate_proj=None, gate_w=None):
     """The serial state recurrence (phase B) on the outputs of phase A -> y [S,16,128] bf16, new state [1,16,128,128] fp32
-    (gdn_nax.py:404-410).  ``Tb, Am, gv`` are what ``prep_a`` / ``phase_a`` returned."""
-    y, st = phase_b_varlen(q.contiguous(), k.contiguous(), v.contiguous(), Tb, gv, init_state=None if state is None else state.contiguous())
+    (gdn_nax.py:404-410).  ``Tb, Am, gv`` are what ``prep_a`` / ``phase_a`` returned.  ``gate_proj`` / ``gate_w`` (additive): apply the
+    layer's gated RMSNorm in the y store, i.e. return what the reference's next line, ``gated_norm(out, proj, gnorm)``, would."""
+    y, st = phase_b_varlen(q.contiguous(), k.contiguous(), v.contiguous(), Tb, gv, init_state=None if state is None else state.contiguous(),
+                           gate_proj=gate_proj, gate_w=gate_w)
     return y, st
 
 

@@ -129,3 +129,41 @@ def test_config3_every_layer_seed(dev, layer):
     assert orc.max_err_scaled(host(s[0])[heads], s_ref) < 1e-4
     assert orc.rel_l2(host(y)[:, heads], y_ref) < 2e-3
     assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("S", [2048, 2000, 37, 5])
+def test_gated_norm_fused_into_phase_b_equals_the_separate_kernel(dev, S):
+    """The reference's layer ends with ``gated_norm(out, proj, gnorm)`` on the output of phase_b (qwen35/prefill.py:253-264).  With the
+    norm applied in phase B's y store the result has the same bits as the two calls, and the state is untouched by the option."""
+    from qwen_tailor_b200.prefill import gated_norm
+    proj, conv, cw, A_log, dtb, st0 = _layer_inputs(dev, S, seed=100 + S)
+    gw = f32_dev(1.0 + 0.1 * np.random.default_rng(S).standard_normal(128).astype(np.float32), dev)
+    q, k, v, Tb, Am, gv = prep_a(proj, conv, cw.reshape(6144, 1, 4), A_log, dtb)
+    y, st = phase_b(q, k, v, Tb, Am, gv, st0)
+    want = gated_norm(y, proj, gw)
+    got, st2 = phase_b(q, k, v, Tb, Am, gv, st0, gate_proj=proj, gate_w=gw)
+    assert torch.equal(got.reshape(S, 2048), want) and torch.equal(st, st2)
+    assert _lib.device_status() == 0
+
+
+def test_gated_norm_fused_on_a_packed_batch_and_head_range(dev):
+    """Packed ragged sequences, a head sub-range: the fused store only touches the rows and heads that the call owns."""
+    from qwen_tailor_b200.prefill import gated_norm
+    lens = [130, 64, 1, 77]
+    T = sum(lens)
+    rng = np.random.default_rng(7)
+    proj = bf16_dev(synth.bf16r(rng.standard_normal((T, 8224))), dev)
+    gw = f32_dev(1.0 + 0.1 * rng.standard_normal(128).astype(np.float32), dev)
+    q = bf16_dev(synth.bf16r(rng.standard_normal((T, 16, 128)) * 0.088), dev)
+    k = bf16_dev(synth.bf16r(rng.standard_normal((T, 16, 128)) * 0.088), dev)
+    v = bf16_dev(synth.bf16r(rng.standard_normal((T, 16, 128))), dev)
+    lg = f32_dev(-np.abs(rng.standard_normal((T, 16))).astype(np.float32) * 0.05, dev)
+    beta = f32_dev(rng.uniform(0.1, 0.9, (T, 16)).astype(np.float32), dev)
+    cu = i32_dev(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32), dev)
+    y, st = gdn_chunked_varlen(q, k, v, lg, beta, cu)
+    want = gated_norm(y, proj, gw).reshape(T, 16, 128)
+    got = torch.full_like(y, 3.0)
+    _, st2 = gdn_chunked_varlen(q, k, v, lg, beta, cu, head_lo=4, head_hi=12, y=got, gate_proj=proj, gate_w=gw)
+    assert torch.equal(got[:, 4:12], want[:, 4:12])
+    assert torch.all(got[:, :4] == 3.0) and torch.all(got[:, 12:] == 3.0)
+    assert torch.equal(st2[:, 4:12], st[:, 4:12])
