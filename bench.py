@@ -301,6 +301,51 @@ def bench_attention(torch, dev, args, peaks, n_layers=6):
                 kv_gb=byts / 1e9, roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"]))
 
 
+def bench_attention_large(torch, dev, args, peaks, B=64, ctx=8192, n_layers=2):
+    """The same kernel on a cache of about a gigabyte per layer (B sequences x ctx keys): the fixed costs of a call -- launch, first
+    tile, read-out, merge -- weigh much less than on configuration 5's 130 MB per layer."""
+    from qwen_tailor_b200.batch import attn_paged
+    M, page = 4, 64
+    per = (ctx + M + page - 1) // page
+    n_pages = B * per + 1
+    g, _ = rn_factory(torch, dev, 13)
+    rn = lambda *s: torch.randn(s, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    layers = [dict(K=rn(n_pages, 2, page, 256), V=rn(n_pages, 2, page, 256), q=rn(B * M, 8, 256), k=rn(B * M, 2, 256), v=rn(B * M, 2, 256))
+              for _ in range(n_layers)]
+    bt = (1 + torch.arange(B * per, dtype=torch.int32, device=dev)).reshape(B, per).contiguous()
+    cl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+
+    def step():
+        for L in layers:
+            attn_paged(L["q"], L["k"], L["v"], L["K"], L["V"], bt, cl, M=M, max_ctx=ctx)
+
+    ms = time_region(torch, graphed(torch, step), args.steps, repeats=3) / args.steps
+    byts = n_layers * float(B * ctx) * 2048
+    gbs = byts / (ms * 1e-3) / 1e9
+    return dict(workload=f"GQA decode attention, B={B}, M=4, ctx={ctx}, {n_layers} layers, paged bf16 KV", ms_per_step=ms, kv_gb=byts / 1e9,
+                roofline=dict(bound="hbm", achieved=gbs, peak=peaks["hbm_gbs"], unit="GB/s", frac=gbs / peaks["hbm_gbs"]))
+
+
+def bench_prefill_attention(torch, dev, args, peaks, S=2048, n_layers=6):
+    """Causal prefill attention of the full-attention layers (head_dim 256, 8 query heads on 2 KV heads): S tokens from position 0,
+    n_layers layers with their own q / K / V.  FLOPs: 4 * 256 per (query head, query, visible key)."""
+    from qwen_tailor_b200.attn_glue import prefill_attention
+    g, _ = rn_factory(torch, dev, 17)
+    rn = lambda *s: torch.randn(s, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    layers = [dict(q=rn(S, 8, 256), K=rn(2, S, 256), V=rn(2, S, 256)) for _ in range(n_layers)]
+
+    def step():
+        for L in layers:
+            prefill_attention(L["q"], L["K"], L["V"], pos=0)
+
+    ms = time_region(torch, graphed(torch, step), args.steps, repeats=3) / args.steps
+    flops = n_layers * 4.0 * 256 * 8 * (S * (S + 1) / 2)
+    tf = flops / (ms * 1e-3) / 1e12
+    return dict(workload=f"causal prefill attention, S={S}, {n_layers} layers, 8 q heads / 2 KV heads, head_dim 256", ms_per_step=ms,
+                tokens_per_s=S / (ms * 1e-3),
+                roofline=dict(bound="tensor", achieved=tf, peak=peaks["bf16_tflops"], unit="TFLOP/s", frac=tf / peaks["bf16_tflops"]))
+
+
 def bench_verify(torch, dev, args, peaks, n_layers=N_LAYERS, B=16):
     """Configuration 5, GDN part: B sequences x M=4 chained tokens through n_layers layers, per-token fp32 snapshots in place."""
     from qwen_tailor_b200.batch_spec import deltanet_bm
@@ -522,6 +567,9 @@ def run_extras(torch, dev, args, peaks, _lib, dist=None):
                 ("verify_config5", lambda: bench_verify(torch, dev, a2, peaks)),
                 ("verify_B64_M4", lambda: bench_verify(torch, dev, a2, peaks, n_layers=6, B=64)),
                 ("attention_config5", lambda: bench_attention(torch, dev, a2, peaks)),
+                ("attention_B64_ctx8192", lambda: bench_attention_large(torch, dev, a2, peaks)),
+                ("prefill_attention_S2048", lambda: bench_prefill_attention(torch, dev, a2, peaks)),
+                ("prefill_attention_S8192", lambda: bench_prefill_attention(torch, dev, a2, peaks, S=8192)),
                 ("prefill_T2048", lambda: bench_prefill(torch, dev, a2, peaks)),
                 ("prefill_T8192", lambda: bench_prefill(torch, dev, a2, peaks, T=8192, n_layers=9, n_sets=2)),
                 ("prefill_T8192_one_sequence", lambda: bench_prefill_single(torch, dev, a2, peaks)),

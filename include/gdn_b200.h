@@ -122,6 +122,17 @@ GDN_API int gdn_phase_b(const void* q, const void* k, const void* v, const void*
                 const float* init_state, const int* init_idx, void* y, float* final_state, int n_seq, long long total_T, int H, int head_lo,
                 int head_hi, void* stream);
 
+/* Causal prefill attention, head_dim 256, 8 query heads on 2 KV heads, on the tensor cores: for the S query tokens at positions
+ * pos .. pos + S - 1, out[i, h, :] = softmax(q[i, h, :] . K[0 .. pos + i, h / 4, :] / 16) V[0 .. pos + i, h / 4, :] (fp32 scores and
+ * accumulation, bf16 in and out).
+ * Replaces: the scaled_dot_product_attention call of the prefill, qwen35/model.py:165 (function :148-169), reached from
+ * qwen35/prefill.py:468; the reference passes q [1,8,S,256] and K / V [1,2,kv_len,256] with a causal mask.
+ *   q, out bf16 [S, 8, 256];  k, v bf16: key t of KV head g at k + t * k_tok_stride + g * k_head_stride (elements), so both the
+ *   reference's [2, T, 256] cache (tok stride 256, head stride T_max * 256) and a [T, 2, 256] layout (512, 256) are accepted; K and V
+ *   must use the same kind of layout; keys 0 .. pos + S - 1 must exist.  Strides are multiples of 8 elements, pointers 16-byte aligned. */
+GDN_API int gqa_prefill_attn(const void* q, const void* k, const void* v, void* out, int S, int pos, long long k_tok_stride, long long k_head_stride,
+                     long long v_tok_stride, long long v_head_stride, void* stream);
+
 /* Phase B with the gated RMSNorm of the layer fused into its y store: y <- bf16(silu(z) * (gate_w * (y * rsqrt(mean(y^2) + 1e-6))))
  * per (token, head) row, computed on the bf16-rounded y exactly as gdn_gated_norm does (same bits as gdn_phase_b followed by
  * gdn_gated_norm), so the y tensor never makes the round trip through memory between the two.

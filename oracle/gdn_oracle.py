@@ -244,6 +244,24 @@ def attn_rows(q, k_new, v_new, k_ctx, v_ctx, dtype=np.float64):
     return out
 
 
+def prefill_attention(q, K, V, pos=0, dtype=np.float64):
+    """Causal attention of a prefill chunk: the scaled_dot_product_attention call of qwen35/model.py:165 (scale D^-1/2, causal mask,
+    GQA: query head h reads KV head h // (H // KV)).
+
+    q [S, H, D]: queries at positions pos .. pos + S - 1; K, V [KV, T, D] with T >= pos + S.  Returns o [S, H, D] in ``dtype`` (unrounded)."""
+    q, K, V = (np.asarray(x, dtype) for x in (q, K, V))
+    S, H, D = q.shape
+    KV = K.shape[0]
+    out = np.zeros((S, H, D), dtype)
+    for h in range(H):
+        kv = h // (H // KV)
+        s = (q[:, h] * dtype(D ** -0.5)) @ K[kv, :pos + S].T                      # [S, pos + S]
+        s = np.where(np.arange(pos + S)[None, :] <= (pos + np.arange(S))[:, None], s, -np.inf)
+        p = np.exp(s - s.max(axis=1, keepdims=True))
+        out[:, h] = (p @ V[kv, :pos + S]) / p.sum(axis=1, keepdims=True)
+    return out
+
+
 def qkv_prep(qkv, q_norm, k_norm, row_pos, eps=1e-6, theta=1e7, rope_dim=64):
     """Attention glue in front of the decode attention (qwen35/fast.py:70-78, qwen35/model.py:148-161): split a qkv row into
     8 x (q 256 | gate 256), k 2 x 256, v 2 x 256; rms_norm q and k over 256 with weights; rotate dims [0, 64) of q and k

@@ -33,3 +33,31 @@ def gate_out(o, gate):
     out = torch.empty_like(o2)
     check(_lib.load().gqa_gate_out(ptr(o2), ptr(g2), ptr(out), o2.numel(), stream_ptr(o.device)), "gate_out")
     return out
+
+
+def prefill_attention(q, K, V, pos=0):
+    """Causal attention of a prefill chunk on the tensor cores: the ``mx.fast.scaled_dot_product_attention(q, K[:, :, :kv_len],
+    V[:, :, :kv_len], scale=256**-0.5, mask="causal")`` of the reference's full-attention layer (qwen35/model.py:165).
+
+    q [S, 8, 256] bf16: the S query tokens at positions pos .. pos + S - 1 (rms-normed and rotated, as ``qkv_prep`` returns them).
+    K, V: the cache including this chunk's rows, either the reference's head-major [2, T, 256] / [1, 2, T, 256] (T >= pos + S) or
+    token-major [T, 2, 256]; any strides that are multiples of 8 elements with a contiguous last dimension.
+    Returns o [S, 8, 256] bf16."""
+    _lib.require_cuda(q, K, V)
+    assert q.dtype == torch.bfloat16 and q.dim() == 3 and tuple(q.shape[1:]) == (8, 256) and q.is_contiguous()
+    S = q.shape[0]
+    if K.dim() == 4:
+        K, V = K[0], V[0]
+    assert K.dtype == torch.bfloat16 and V.dtype == torch.bfloat16 and K.dim() == 3 and K.shape == V.shape and K.shape[2] == 256
+    assert K.stride(2) == 1 and V.stride(2) == 1
+    if K.shape[0] == 2 and K.shape[1] != 2:                         # [2, T, 256]
+        T, ks, vs = K.shape[1], (K.stride(1), K.stride(0)), (V.stride(1), V.stride(0))
+    elif K.shape[1] == 2:                                           # [T, 2, 256]
+        T, ks, vs = K.shape[0], (K.stride(0), K.stride(1)), (V.stride(0), V.stride(1))
+    else:
+        raise ValueError(f"prefill_attention: K must be [2, T, 256] or [T, 2, 256], got {tuple(K.shape)}")
+    if T < pos + S:
+        raise ValueError(f"prefill_attention: the cache holds {T} keys, pos + S = {pos + S}")
+    out = torch.empty_like(q)
+    check(_lib.load().gqa_prefill_attn(ptr(q), ptr(K), ptr(V), ptr(out), S, int(pos), ks[0], ks[1], vs[0], vs[1], stream_ptr(q.device)), "prefill_attention")
+    return out

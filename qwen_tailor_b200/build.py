@@ -13,7 +13,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libgdn_b200.so"
-SOURCES = ["c_api.cu", "gdn_decode.cu", "gdn_recurrent.cu", "gqa_decode.cu", "gqa_decode_tc.cu", "state_copy.cu", "gdn_phase_a.cu", "gdn_prefill_sm100.cu",
+SOURCES = ["c_api.cu", "gdn_decode.cu", "gdn_recurrent.cu", "gqa_decode.cu", "gqa_decode_tc.cu", "gqa_prefill_tc.cu", "state_copy.cu", "gdn_phase_a.cu", "gdn_prefill_sm100.cu",
            "attn_glue.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 

@@ -111,6 +111,10 @@ int launch_conv_prep(const __nv_bfloat16* proj, long long row_stride, const __nv
 int launch_gated_norm(const __nv_bfloat16* y, const __nv_bfloat16* proj, long long row_stride, const float* gw, __nv_bfloat16* out, long long S,
                       cudaStream_t st);
 
+// ---- gqa_prefill_tc.cu ----
+int launch_gqa_prefill(const void* q, const void* k, const void* v, void* out, int S, int pos, long long k_tok_stride, long long k_head_stride,
+                       long long v_tok_stride, long long v_head_stride, int* status, cudaStream_t stream);
+
 // ---- state_copy.cu ----
 int launch_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,
                       long long sstride, cudaStream_t st);
