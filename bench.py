@@ -611,7 +611,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--extras-child", action="store_true", help="run only the additional single-GPU workloads and print them as one JSON object")
     ap.add_argument("--only", default=None, help="comma-separated names of the additional workloads to run (with --extras-child)")
-    ap.add_argument("--case", default=None, choices=["prefill", "attention", "verify", "decode"],
+    ap.add_argument("--case", default=None, choices=["prefill", "attention", "verify", "decode", "prefill_attention"],
                     help="run only this small workload a few times and print its line (used for ncu captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -641,6 +641,8 @@ def main():
             out = bench_prefill(torch, dev, a2, peaks, n_layers=9, n_sets=1)     # 9 x 16 chains = one wave of 144 blocks, 0.3 GB of inputs
         elif args.case == "attention":
             out = bench_attention(torch, dev, a2, peaks, n_layers=2)
+        elif args.case == "prefill_attention":
+            out = bench_prefill_attention(torch, dev, a2, peaks, S=4096, n_layers=1)
         elif args.case == "decode":
             d = bench_decode(torch, dev, a2, None, peaks, n_layers=4, with_e2e=False)
             out = dict(launch_us=d["launch_us"], hbm_gbs=d["achieved_gbs"], frac=d["frac"])
