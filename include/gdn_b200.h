@@ -129,9 +129,14 @@ GDN_API int gdn_phase_b(const void* q, const void* k, const void* v, const void*
  * qwen35/prefill.py:468; the reference passes q [1,8,S,256] and K / V [1,2,kv_len,256] with a causal mask.
  *   q, out bf16 [S, 8, 256];  k, v bf16: key t of KV head g at k + t * k_tok_stride + g * k_head_stride (elements), so both the
  *   reference's [2, T, 256] cache (tok stride 256, head stride T_max * 256) and a [T, 2, 256] layout (512, 256) are accepted; K and V
- *   must use the same kind of layout; keys 0 .. pos + S - 1 must exist.  Strides are multiples of 8 elements, pointers 16-byte aligned. */
+ *   must use the same kind of layout; keys 0 .. pos + S - 1 must exist.  Strides are multiples of 8 elements, pointers 16-byte aligned.
+ *   workspace (optional, may be NULL): with gqa_prefill_attn_workspace_bytes(S, pos) bytes (16-byte aligned, contents need no
+ *   initialisation, not shared by calls that overlap on the GPU) the query blocks with the most keys are split in two along the keys
+ *   and merged in the kernel, which shortens the launch when S is too small to give every SM several blocks; the function returns 0
+ *   bytes for shapes that are not split.  Results with and without a workspace agree to rounding (different summation order). */
 GDN_API int gqa_prefill_attn(const void* q, const void* k, const void* v, void* out, int S, int pos, long long k_tok_stride, long long k_head_stride,
-                     long long v_tok_stride, long long v_head_stride, void* stream);
+                     long long v_tok_stride, long long v_head_stride, void* workspace, size_t workspace_bytes, void* stream);
+GDN_API size_t gqa_prefill_attn_workspace_bytes(int S, int pos);
 
 /* Phase B with the gated RMSNorm of the layer fused into its y store: y <- bf16(silu(z) * (gate_w * (y * rsqrt(mean(y^2) + 1e-6))))
  * per (token, head) row, computed on the bf16-rounded y exactly as gdn_gated_norm does (same bits as gdn_phase_b followed by

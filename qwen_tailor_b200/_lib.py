@@ -42,7 +42,8 @@ SIGNATURES = {
     "gqa_decode_paged_static": (I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]),
     "gqa_qkv_prep": (I, [P, LL, P, P, P, P, P, P, P, I, F, F, P]),
     "gqa_gate_out": (I, [P, P, P, LL, P]),
-    "gqa_prefill_attn": (I, [P, P, P, P, I, I, LL, LL, LL, LL, P]),
+    "gqa_prefill_attn": (I, [P, P, P, P, I, I, LL, LL, LL, LL, P, SZ, P]),
+    "gqa_prefill_attn_workspace_bytes": (SZ, [I, I]),
     "gdn_conv_prep": (I, [P, LL, P, P, P, P, P, P, I, P]),
     "gdn_gated_norm": (I, [P, P, LL, P, P, LL, P]),
     "gdn_state_copy": (I, [P, P, I, LL, LL, LL, I, LL, LL, P]),

@@ -35,13 +35,16 @@ def gate_out(o, gate):
     return out
 
 
-def prefill_attention(q, K, V, pos=0):
+def prefill_attention(q, K, V, pos=0, split=False):
     """Causal attention of a prefill chunk on the tensor cores: the ``mx.fast.scaled_dot_product_attention(q, K[:, :, :kv_len],
     V[:, :, :kv_len], scale=256**-0.5, mask="causal")`` of the reference's full-attention layer (qwen35/model.py:165).
 
     q [S, 8, 256] bf16: the S query tokens at positions pos .. pos + S - 1 (rms-normed and rotated, as ``qkv_prep`` returns them).
     K, V: the cache including this chunk's rows, either the reference's head-major [2, T, 256] / [1, 2, T, 256] (T >= pos + S) or
     token-major [T, 2, 256]; any strides that are multiples of 8 elements with a contiguous last dimension.
+    ``split`` (additive, off by default): let the kernel split the query blocks with the most keys in two along the keys (a scratch
+    tensor is allocated) so that short prefills, where the causal triangle leaves SMs idle behind the last query block, spread
+    better; on B200 the partials' round trip through memory costs about what the better balance gains (S = 2048: 58 against 60 us).
     Returns o [S, 8, 256] bf16."""
     _lib.require_cuda(q, K, V)
     assert q.dtype == torch.bfloat16 and q.dim() == 3 and tuple(q.shape[1:]) == (8, 256) and q.is_contiguous()
@@ -59,5 +62,9 @@ def prefill_attention(q, K, V, pos=0):
     if T < pos + S:
         raise ValueError(f"prefill_attention: the cache holds {T} keys, pos + S = {pos + S}")
     out = torch.empty_like(q)
-    check(_lib.load().gqa_prefill_attn(ptr(q), ptr(K), ptr(V), ptr(out), S, int(pos), ks[0], ks[1], vs[0], vs[1], stream_ptr(q.device)), "prefill_attention")
+    lib = _lib.load()
+    ws_bytes = int(lib.gqa_prefill_attn_workspace_bytes(S, int(pos))) if split and S > 0 else 0
+    ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=q.device) if ws_bytes else None
+    check(lib.gqa_prefill_attn(ptr(q), ptr(K), ptr(V), ptr(out), S, int(pos), ks[0], ks[1], vs[0], vs[1], ptr(ws), ws_bytes, stream_ptr(q.device)),
+          "prefill_attention")
     return out

@@ -296,8 +296,10 @@ int gqa_gate_out(const void* o, const void* gate, void* out, long long n, void* 
     return launch_gate_out((const __nv_bfloat16*)o, (const __nv_bfloat16*)gate, (__nv_bfloat16*)out, n, static_cast<cudaStream_t>(stream));
 }
 
+size_t gqa_prefill_attn_workspace_bytes(int S, int pos) { return S > 0 && pos >= 0 ? gdn::gqa_prefill_workspace_bytes(S, pos) : 0; }
+
 int gqa_prefill_attn(const void* q, const void* k, const void* v, void* out, int S, int pos, long long k_tok_stride, long long k_head_stride,
-                     long long v_tok_stride, long long v_head_stride, void* stream) {
+                     long long v_tok_stride, long long v_head_stride, void* workspace, size_t workspace_bytes, void* stream) {
     REQUIRE(q && k && v && out, GDN_E_NULL, "gqa_prefill_attn: null pointer");
     REQUIRE(S >= 0 && pos >= 0 && (long long)pos + S < (1ll << 30), GDN_E_SHAPE, "gqa_prefill_attn: S=%d pos=%d", S, pos);
     REQUIRE(k_tok_stride > 0 && k_head_stride > 0 && v_tok_stride > 0 && v_head_stride > 0 && k_tok_stride % 8 == 0 && k_head_stride % 8 == 0 &&
@@ -307,7 +309,9 @@ int gqa_prefill_attn(const void* q, const void* k, const void* v, void* out, int
     if (S == 0) return GDN_OK;
     int* status = status_ptr();
     REQUIRE(status, GDN_E_LAUNCH, "gqa_prefill_attn: no CUDA device");
-    return launch_gqa_prefill(q, k, v, out, S, pos, k_tok_stride, k_head_stride, v_tok_stride, v_head_stride, status, static_cast<cudaStream_t>(stream));
+    REQUIRE(!workspace || aligned16(workspace), GDN_E_ALIGN, "gqa_prefill_attn: workspace must be 16-byte aligned");
+    return launch_gqa_prefill(q, k, v, out, S, pos, k_tok_stride, k_head_stride, v_tok_stride, v_head_stride, workspace, workspace_bytes, status,
+                              static_cast<cudaStream_t>(stream));
 }
 
 int gdn_conv_prep(const void* proj, long long row_stride, const void* conv_state, const void* conv_w, void* q, void* k, void* v, void* new_conv,

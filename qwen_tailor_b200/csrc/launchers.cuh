@@ -113,7 +113,8 @@ int launch_gated_norm(const __nv_bfloat16* y, const __nv_bfloat16* proj, long lo
 
 // ---- gqa_prefill_tc.cu ----
 int launch_gqa_prefill(const void* q, const void* k, const void* v, void* out, int S, int pos, long long k_tok_stride, long long k_head_stride,
-                       long long v_tok_stride, long long v_head_stride, int* status, cudaStream_t stream);
+                       long long v_tok_stride, long long v_head_stride, void* workspace, size_t workspace_bytes, int* status, cudaStream_t stream);
+size_t gqa_prefill_workspace_bytes(int S, int pos);
 
 // ---- state_copy.cu ----
 int launch_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,

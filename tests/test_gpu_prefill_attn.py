@@ -26,7 +26,7 @@ def _qkv(S, T, seed, spread=1.0):
 @pytest.mark.parametrize("S,pos", [(1, 0), (5, 0), (31, 0), (32, 0), (33, 0), (64, 0), (100, 0), (257, 0), (2048, 0), (1, 77), (40, 24), (96, 1000), (300, 333)])
 def test_prefill_attention_matches_the_oracle(dev, S, pos):
     q, K, V = _qkv(S, pos + S, seed=S * 7 + pos)
-    o = prefill_attention(bf16_dev(q, dev), bf16_dev(K, dev), bf16_dev(V, dev), pos=pos)
+    o = prefill_attention(bf16_dev(q, dev), bf16_dev(K, dev), bf16_dev(V, dev), pos=pos, split=(S + pos) % 2 == 0)
     ref = orc.prefill_attention(q, K, V, pos)
     assert _lib.device_status() == 0
     got = host(o)
@@ -104,3 +104,28 @@ def test_prefill_attention_rejects_bad_arguments(dev):
         prefill_attention(qd, Kd, Vd, pos=4)                           # the cache is too short for pos + S
     with pytest.raises(ValueError):
         prefill_attention(qd, torch.zeros((3, 8, 256), dtype=torch.bfloat16, device=dev), torch.zeros((3, 8, 256), dtype=torch.bfloat16, device=dev))      # neither layout
+
+
+def test_split_blocks_agree_with_unsplit_and_the_workspace_needs_no_reset(dev):
+    """With a workspace the heaviest query blocks run as two blocks along the keys and are merged by the half that arrives last.
+    Same result as the unsplit launch to rounding; the workspace's arrival counters carry an epoch tag, so one workspace -- filled with
+    garbage at first -- serves call after call without being cleared."""
+    from qwen_tailor_b200._lib import check, load, ptr, stream_ptr
+    S = 1024
+    q, K, V = _qkv(S, S, seed=41)
+    qd, Kd, Vd = bf16_dev(q, dev), bf16_dev(K, dev), bf16_dev(V, dev)
+    plain = prefill_attention(qd, Kd, Vd, split=False)
+    lib = load()
+    nbytes = int(lib.gqa_prefill_attn_workspace_bytes(S, 0))
+    assert nbytes > 0 and int(lib.gqa_prefill_attn_workspace_bytes(16384, 0)) == 0      # long prefills have enough blocks: never split
+    ws = torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device=dev)
+    outs = []
+    for _ in range(3):
+        out = torch.empty_like(qd)
+        check(lib.gqa_prefill_attn(ptr(qd), ptr(Kd), ptr(Vd), ptr(out), S, 0, 256, S * 256, 256, S * 256, ptr(ws), nbytes, stream_ptr(dev)), "prefill")
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert orc.rel_l2(host(outs[0]), host(plain).astype(np.float64)) <= 1e-3
+    assert orc.rel_l2(host(outs[0]), orc.prefill_attention(q, K, V, 0)) <= TOL_REL_L2
+    assert _lib.device_status() == 0
