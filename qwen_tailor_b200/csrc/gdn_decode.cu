@@ -46,10 +46,20 @@ struct SeqPtrs {
     bool ok;
 };
 
-__device__ __forceinline__ SeqPtrs resolve(const DecodeArgs& a, int b) {
+// the index words of sequence b, as loaded (the loads are independent of one another: issuing them costs nothing until a value is used)
+struct RawIdx { int e, i1, i2; };
+__device__ __forceinline__ RawIdx load_idx(const DecodeArgs& a, int b) {
+    RawIdx r;
+    r.e = a.i0[a.mode == 0 ? 0 : b];
+    r.i1 = a.mode == 0 ? 0 : a.i1[b];
+    r.i2 = a.mode == 2 ? a.i2[b] : 0;
+    return r;
+}
+
+__device__ __forceinline__ SeqPtrs make_ptrs(const DecodeArgs& a, const RawIdx& r) {
     SeqPtrs p;
     const int M = a.M;
-    const int e = a.i0[a.mode == 0 ? 0 : b];
+    const int e = r.e;
     p.ok = e >= 0 && e < a.n_entries;
     const size_t es = p.ok ? (size_t)e : 0;
     if (a.mode == 0) {
@@ -58,15 +68,15 @@ __device__ __forceinline__ SeqPtrs resolve(const DecodeArgs& a, int b) {
         p.st_in = a.ssm_pool + es * STATE_ELEMS;
         p.st_out = a.ssm_out;
     } else if (a.mode == 1) {
-        const unsigned par = (unsigned)a.i1[b] & 1u;
+        const unsigned par = (unsigned)r.i1 & 1u;
         p.cs_in = a.conv_pool + (es * 2 + par) * 3 * CD;
         p.cs_out = a.conv_pool + (es * 2 + (par ^ 1u)) * 3 * CD;
         p.st_in = a.ssm_pool + es * STATE_ELEMS;
         p.st_out = a.ssm_pool + es * STATE_ELEMS;
     } else {
-        int sl = a.i1[b];
+        int sl = r.i1;
         if (sl < 0 || sl >= M) { p.ok = false; sl = 0; }
-        const unsigned par = (unsigned)a.i2[b] & 1u;
+        const unsigned par = (unsigned)r.i2 & 1u;
         p.cs_in = a.conv_pool + ((es * 2 + par) * M + sl) * 3 * CD;
         p.cs_out = a.conv_pool + ((es * 2 + (par ^ 1u)) * M) * 3 * CD;
         p.st_out = a.ssm_pool + es * M * STATE_ELEMS;
@@ -74,6 +84,7 @@ __device__ __forceinline__ SeqPtrs resolve(const DecodeArgs& a, int b) {
     }
     return p;
 }
+__device__ __forceinline__ SeqPtrs resolve(const DecodeArgs& a, int b) { return make_ptrs(a, load_idx(a, b)); }
 
 // raw inputs of one thread's three channels (q, k, v channel `tid` of a head) for MT chained tokens
 // (kept as raw bf16 bits: converting at the point of use keeps the loads asynchronous when they are issued one head ahead)
@@ -130,26 +141,45 @@ __global__ void __launch_bounds__(128, Tune<MT>::BLOCKS) gdn_decode_kernel(const
     }
     __syncthreads();
 
-    auto issue = [&](int idx) {                         // thread 0: start the copy of slice `idx` into its ring stage
+    // thread 0: start the copy of slice `idx` into its ring stage; st_in = the state of the slice's sequence
+    auto issue = [&](int idx, const float* st_in) {
         const int n = idx - lo, stage = n % NST;
-        const int b = idx / (HV * SLICES_PER_HEAD), hv = (idx / SLICES_PER_HEAD) % HV, sl = idx % SLICES_PER_HEAD;
-        const SeqPtrs sp = resolve(a, b);
-        const float* src = sp.st_in + ((size_t)hv * DV + sl * SLICE_ROWS) * DK;
+        const int hv = (idx / SLICES_PER_HEAD) % HV, sl = idx % SLICES_PER_HEAD;
+        const float* src = st_in + ((size_t)hv * DV + sl * SLICE_ROWS) * DK;
         const uint32_t bar = sm100::smem_addr(&full_bar[stage]);
         sm100::mbar_expect_tx(bar, SLICE_BYTES);
         bulk_load(sm100::smem_addr(ring + stage * SLICE_FLOATS), src, SLICE_BYTES, bar);
     };
-    if (tid == 0)
-        for (int i = lo; i < hi && i < lo + NST; i++) issue(i);
 
     const float inv_scale = 0.08838834764831845f;          // 128^-1/2
     const float e2 = 1e-6f * inv_scale * inv_scale;
     const float sc_q = bf(inv_scale * inv_scale), sc_k = bf(inv_scale);
 
+    GDN_BSTAMP(0);
+    // Everything a head's prologue needs -- the sequence's pointers included -- is fetched into registers one head ahead (`nxt*`):
+    // a load issued while the bulk copies saturate the memory system takes microseconds (measured: 3.5 us for the first index word
+    // when it was issued behind the ring's copies, and 3 us per further head of a block for the same word), so neither the prologue
+    // nor the thread that refills the ring may wait for one.  For the first head the loads go out before the ring's copies.
+    // (Loading the index words two heads ahead, so that the prefetch itself never waits for them, measured 1.5% slower.)
     HeadInputs<MT> nxt;
+    SeqPtrs nxt_sp{};
+    float nxt_alog = 0.f, nxt_dtb = 0.f;
     int have_b = -1, have_hv = -1;                         // head whose inputs sit in `nxt`
     int cur_b = -1, cur_hv = -1;
     SeqPtrs sp{};
+    auto prefetch_head = [&](int pb, int phv) {
+        nxt_sp = resolve(a, pb);
+        fetch_head<MT>(a, nxt_sp, pb, phv, tid, nxt);
+        nxt_alog = a.A_log[phv];
+        nxt_dtb = a.dt_bias[phv];
+        have_b = pb; have_hv = phv;
+    };
+    prefetch_head(lo / (HV * SLICES_PER_HEAD), (lo / SLICES_PER_HEAD) % HV);
+    if (tid == 0)
+        for (int i = lo; i < hi && i < lo + NST; i++) {
+            const int ib = i / (HV * SLICES_PER_HEAD);
+            issue(i, ib == have_b ? nxt_sp.st_in : resolve(a, ib).st_in);
+        }
 
     for (int idx = lo; idx < hi; idx++) {
         const int n = idx - lo, stage = n % NST;
@@ -158,25 +188,21 @@ __global__ void __launch_bounds__(128, Tune<MT>::BLOCKS) gdn_decode_kernel(const
         if (b != cur_b || hv != cur_hv) {
             // ---- prologue of a new head: conv + silu, l2norm, gates for the M tokens, conv-window snapshots ----
             cur_b = b; cur_hv = hv;
-            sp = resolve(a, b);
+            if (have_b != b || have_hv != hv) prefetch_head(b, hv);      // (does not happen: every head is fetched one head ahead)
+            sp = nxt_sp;
+            const HeadInputs<MT> in = nxt;
+            const float alog = nxt_alog, dtb = nxt_dtb;
             if (!sp.ok && tid == 0) atomicExch(a.status, 1);
-            HeadInputs<MT> in;
-            if (have_b == b && have_hv == hv) in = nxt;
-            else fetch_head<MT>(a, sp, b, hv, tid, in);
+            if (idx == lo) GDN_BSTAMP(10);
             // start fetching the next head of this block's range while this one is processed
             {
                 const int nidx = (idx / SLICES_PER_HEAD + 1) * SLICES_PER_HEAD;
-                if (nidx < hi) {
-                    const int nb = nidx / (HV * SLICES_PER_HEAD), nhv = (nidx / SLICES_PER_HEAD) % HV;
-                    const SeqPtrs nsp = resolve(a, nb);
-                    fetch_head<MT>(a, nsp, nb, nhv, tid, nxt);
-                    have_b = nb; have_hv = nhv;
-                }
+                if (nidx < hi) prefetch_head(nidx / (HV * SLICES_PER_HEAD), (nidx / SLICES_PER_HEAD) % HV);
             }
             __syncthreads();                               // previous head's readers of sq/sk/sv are done
+            if (idx == lo) GDN_BSTAMP(11);
             float qv[MT], kv[MT];
-            const float expA = expf(a.A_log[hv]);
-            const float dtb = a.dt_bias[hv];
+            const float expA = expf(alog);
 #pragma unroll
             for (int j = 0; j < MT; j++) {
                 if (j < M) {
@@ -233,10 +259,12 @@ __global__ void __launch_bounds__(128, Tune<MT>::BLOCKS) gdn_decode_kernel(const
                 }
             }
             // (the barrier inside the slice step below orders these writes before their readers)
+            if (idx == lo) GDN_BSTAMP(1);
         }
 
         // ---- state slice: shared memory -> registers, then give the stage back to the copy engine ----
         const bool arrived = sm100::mbar_wait(sm100::smem_addr(&full_bar[stage]), (uint32_t)(n / NST) & 1u);
+        if (n < 4) GDN_BSTAMP(2 + 2 * n);
         float4 s[2][4];
         int rows[2];
         const float* sl_base = ring + stage * SLICE_FLOATS;
@@ -247,7 +275,11 @@ __global__ void __launch_bounds__(128, Tune<MT>::BLOCKS) gdn_decode_kernel(const
             for (int i = 0; i < 4; i++) s[p][i] = *reinterpret_cast<const float4*>(sl_base + rows[p] * DK + l8 * 4 + 32 * i);
         }
         __syncthreads();
-        if (tid == 0 && idx + NST < hi) issue(idx + NST);
+        if (tid == 0 && idx + NST < hi) {
+            // the slice three ahead lies in this head or in the next one, whose pointers are in registers already
+            const int ib = (idx + NST) / (HV * SLICES_PER_HEAD);
+            issue(idx + NST, ib == cur_b ? sp.st_in : (ib == have_b ? nxt_sp.st_in : resolve(a, ib).st_in));
+        }
         if (!arrived) { if (tid == 0) atomicExch(a.status, 2); continue; }
         if (!sp.ok) continue;
 
@@ -289,6 +321,8 @@ __global__ void __launch_bounds__(128, Tune<MT>::BLOCKS) gdn_decode_kernel(const
                 if (l8 == 0) yb[(size_t)j * (HV * DV) + rows[p]] = __float2bfloat16_rn(yv);
             }
         }
+        if (n < 4) GDN_BSTAMP(3 + 2 * n);
+        if (idx == hi - 1) GDN_BSTAMP(13);
     }
 }
 
@@ -328,3 +362,9 @@ int launch_decode(const DecodeArgs& a, cudaStream_t stream) {
 }
 
 }  // namespace gdn
+
+#ifdef GDN_TIMING
+extern "C" __attribute__((visibility("default"))) int gdn_timing_log_e(long long* out_host, int n) {
+    return cudaMemcpyFromSymbol(out_host, gdn::g_tlog, sizeof(long long) * n) == cudaSuccess ? 0 : -5;
+}
+#endif
