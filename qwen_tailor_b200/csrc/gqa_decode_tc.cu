@@ -238,6 +238,19 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
         while (l < r) { const int m = (l + r + 1) >> 1; if (cum[m] <= lo) l = m; else r = m - 1; }
         pair = l;
     }
+    // work of this block in pair pr, from tile l on: the tiles past the pair's last real one are the plan's weight of its epilogue
+    auto seg_tiles = [&](int pr, long long l) -> int {
+        const int ta = (int)(l - cum[pr]), tbk = (int)(min(hi, (long long)cum[pr + 1]) - cum[pr]);
+        return max(0, min(tbk, (ctxv[pr / ATT_KV] + TK - 1) / TK + 1) - ta);
+    };
+    auto next_seg = [&](int pr, long long l, int& npair, int& nta) -> bool {      // first segment with work after (pr, l); l = its start
+        for (pr++; l < hi; pr++) {
+            if (cum[pr + 1] <= l) continue;
+            if (seg_tiles(pr, l) > 0) { npair = pr; nta = (int)(l - cum[pr]); return true; }
+            l = min(hi, (long long)cum[pr + 1]);
+        }
+        return false;
+    };
     // the three consumer warps synchronise among themselves; the producer runs ahead on its own, across pair boundaries
     auto csync = [&]() { asm volatile("bar.sync 1, 96;" ::: "memory"); };
     const int ctid = warp < 2 ? tid : tid - 32;                      // 0..95 over warps 0, 1, 3
@@ -246,6 +259,8 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
         // ================= producer: keep the ring full with every tile of this block's range, pair after pair =================
         uint32_t n = 0;
         long long plo = lo;
+        int ahead_page = 0;                                          // this lane's page number for the next segment's first 32 tiles
+        bool have_pages = false;
         // the cache is read once per call: its lines are the first to leave L2, so that the plan, the page table, the partials and
         // the code stay there while hundreds of megabytes stream through
         uint64_t stream_policy;
@@ -260,13 +275,21 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
             const int all_ctx = (ctx + TK - 1) / TK;
             const int ctx_tiles = max(0, min(tbk, all_ctx) - ta);
             const int ntiles = max(0, min(tbk, all_ctx + 1) - ta);         // tiles past all_ctx are the plan's weight of the epilogue: no work
-            const int* table = a.block_table + (size_t)b * a.max_pages;
             bool okp = true;
             int my_page = 0;
+            // page numbers, one lane per tile, 32 tiles at a time.  Those of a segment's first 32 tiles were requested while the
+            // previous segment streamed (a load issued under the copies takes microseconds, and the ring only holds three tiles).
+            auto pages_of = [&](int pr, int first_tile) -> int {         // this lane's page of tile first_tile + lane of pair pr
+                const int pctx = ctxv[pr / ATT_KV];
+                const int e = (int)(((long long)(first_tile + lane) * TK) / a.page_size);
+                return (first_tile + lane < (pctx + TK - 1) / TK && e < a.max_pages) ? a.block_table[(size_t)(pr / ATT_KV) * a.max_pages + e] : 0;
+            };
+            int npair = 0, nta = 0;
+            const bool has_next = next_seg(pp, seg_end, npair, nta);
             for (int t = 0; t < ntiles && okp; t++, n++) {
-                if ((t & 31) == 0) {                                     // page numbers of the next 32 tiles, one lane each
-                    const int e = (int)(((long long)(ta + t + lane) * TK) / a.page_size);
-                    my_page = (t + lane < ctx_tiles && e < a.max_pages) ? table[e] : 0;
+                if ((t & 31) == 0) {
+                    my_page = (t == 0 && have_pages) ? ahead_page : pages_of(pp, ta + t);
+                    if (t == 0) { have_pages = has_next; if (has_next) ahead_page = pages_of(npair, nta); }
                 }
                 int page = __shfl_sync(0xffffffffu, my_page, t & 31);
                 const int stage = n % ATT_STAGES;
@@ -309,19 +332,6 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
     } else {
     uint32_t n0 = 0;                                                 // tiles this block has put through the ring before the current pair
     uint32_t pairs_done = 0, merges_done = 0;                       // pairs seen; merges that went through the ring
-    // work of this block in pair pr, from tile l on: the tiles past the pair's last real one are the plan's weight of its epilogue
-    auto seg_tiles = [&](int pr, long long l) -> int {
-        const int ta = (int)(l - cum[pr]), tbk = (int)(min(hi, (long long)cum[pr + 1]) - cum[pr]);
-        return max(0, min(tbk, (ctxv[pr / ATT_KV] + TK - 1) / TK + 1) - ta);
-    };
-    auto next_seg = [&](int pr, long long l, int& npair, int& nta) -> bool {      // first segment with work after (pr, l); l = its start
-        for (pr++; l < hi; pr++) {
-            if (cum[pr + 1] <= l) continue;
-            if (seg_tiles(pr, l) > 0) { npair = pr; nta = (int)(l - cum[pr]); return true; }
-            l = min(hi, (long long)cum[pr + 1]);
-        }
-        return false;
-    };
     // warp 3 keeps the Q rows of the next pair in registers: fetched while the current pair streams (a load issued then takes
     // microseconds, the memory system being saturated by the copies), written to the operand slabs when the tensor pipe is done
     uint4 qreg[16];
@@ -364,7 +374,6 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
         const long long seg_end = min(hi, (long long)cum[pair + 1]);
         const int ta = (int)(lo - cum[pair]), tbk = (int)(seg_end - cum[pair]);      // this block's tiles of the pair: [ta, tbk)
         const int slot = s_base[pair] + ((int)blockIdx.x - first_block(pair));
-        if (ctid == 0) touch(1 + pair);
         int npair = 0, nta = 0;
         const bool has_next = next_seg(pair, seg_end, npair, nta);  // (the same answer in every thread)
         lo = seg_end;
@@ -574,6 +583,7 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
             tc_fence_before_sync();
         } else if (warp == 3) {
             // ================= look-ahead: the next pair's Q rows (and its append) while this one streams =================
+            if (lane == 0) { touch(1 + pair); __threadfence(); }     // (not on the softmax warp: under the copies this takes microseconds)
             q_have = has_next;
             if (has_next) { q_fetch(npair); if (nta == 0) append(npair); }
         }
