@@ -135,3 +135,62 @@ def test_blit_and_pools_round_trip(dev):
     assert all(torch.equal(a[0][:, :, :pos], b[0][:, :, :pos]) and torch.equal(a[1][:, :, :pos], b[1][:, :, :pos]) for a, b in zip(back["kv"], st["kv"]))
     assert all(float(P.ssm[i][0].abs().sum()) == 0 and float(P.ssm[i][3].abs().sum()) == 0 for i in range(18))
     assert P.nbytes() == 4 * Pools.slot_bytes(cfg, 256)
+
+
+def _check_case(dev, c, ctx, M, page_size, o):
+    for b in range(len(ctx)):
+        n = int(ctx[b])
+        pages = c["block_table"][b]
+        gather = lambda Pg: np.concatenate([Pg[p] for p in pages], axis=1)[:, :n]
+        r = slice(b * M, (b + 1) * M)
+        _check_rows(o[r], c["q"][r], c["k_new"][r], c["v_new"][r], gather(c["k_pages"]), gather(c["v_pages"]), M)
+
+
+@pytest.mark.parametrize("ctx,M", [([0], 1), ([0, 0, 1], 4), ([63, 64, 65], 2), ([1, 127, 128, 129, 3], 3)])
+def test_attn_tiny_contexts_fewer_tiles_than_blocks(dev, ctx, M):
+    """Empty and one-tile contexts on 64-key pages (the tensor-core kernel): only a few of the persistent blocks get any work, the
+    others leave at once; a pair's only tile may be the one that holds this call's own rows."""
+    rng = np.random.default_rng(100 + len(ctx) + M)
+    c = synth.attn_case(rng, ctx, M, 64)
+    o = attn_paged(bf16_dev(c["q"], dev), bf16_dev(c["k_new"], dev), bf16_dev(c["v_new"], dev), bf16_dev(c["k_pages"], dev),
+                   bf16_dev(c["v_pages"], dev), i32_dev(c["block_table"], dev), i32_dev(c["ctx_len"], dev), M=M)
+    _check_case(dev, c, ctx, M, 64, o)
+    assert _lib.device_status() == 0
+
+
+def test_attn_more_sequences_than_the_tensor_core_kernel_plans_for(dev):
+    """300 sequences = 600 (sequence, KV head) pairs: beyond the 512 pairs the tcgen05 kernel plans for in shared memory, so the call
+    is served by the plan kernel + mma.sync kernel with TMA tile loads; same results."""
+    rng = np.random.default_rng(77)
+    ctx = rng.integers(1, 200, 300)
+    c = synth.attn_case(rng, ctx, 1, 64)
+    o = attn_paged(bf16_dev(c["q"], dev), bf16_dev(c["k_new"], dev), bf16_dev(c["v_new"], dev), bf16_dev(c["k_pages"], dev),
+                   bf16_dev(c["v_pages"], dev), i32_dev(c["block_table"], dev), i32_dev(c["ctx_len"], dev), M=1)
+    sel = [0, 1, 150, 299]
+    for b in sel:
+        n = int(ctx[b])
+        pages = c["block_table"][b]
+        gather = lambda Pg: np.concatenate([Pg[p] for p in pages], axis=1)[:, :n]
+        _check_rows(o[b:b + 1], c["q"][b:b + 1], c["k_new"][b:b + 1], c["v_new"][b:b + 1], gather(c["k_pages"]), gather(c["v_pages"]), 1)
+    assert _lib.device_status() == 0
+
+
+def test_attn_one_workspace_serves_calls_of_different_shapes(dev):
+    """The arrival counters in the workspace carry an epoch tag: a workspace that starts as garbage and is reused by calls with
+    different batches and contexts -- so that a pair's number of partials changes from call to call -- needs no clearing."""
+    from qwen_tailor_b200._lib import check, load, ptr, stream_ptr
+    lib = load()
+    ws_bytes = int(lib.gqa_decode_workspace_bytes(8, 8192))
+    ws = torch.randint(0, 255, (ws_bytes,), dtype=torch.uint8, device=dev)
+    for seed, ctx in enumerate(([8192, 40], [300, 5000, 77, 2048, 64, 1], [4000], [8192, 40])):
+        rng = np.random.default_rng(200 + seed)
+        M = 4
+        c = synth.attn_case(rng, ctx, M, 64)
+        q, kn, vn = bf16_dev(c["q"], dev), bf16_dev(c["k_new"], dev), bf16_dev(c["v_new"], dev)
+        Kd, Vd = bf16_dev(c["k_pages"], dev), bf16_dev(c["v_pages"], dev)
+        bt, cl = i32_dev(c["block_table"], dev), i32_dev(c["ctx_len"], dev)
+        o = torch.empty_like(q)
+        check(lib.gqa_decode_paged(ptr(q), ptr(kn), ptr(vn), ptr(Kd), ptr(Vd), ptr(bt), ptr(cl), ptr(o), ptr(ws), ws_bytes, len(ctx), M, 64,
+                                   bt.shape[1], Kd.shape[0], int(max(ctx)), stream_ptr(dev)), "gqa_decode_paged")
+        _check_case(dev, c, ctx, M, 64, o)
+    assert _lib.device_status() == 0
