@@ -628,6 +628,8 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    from qwen_tailor_b200.shard import bind_host_to_gpu
+    host_binding = bind_host_to_gpu(local)               # pinned buffers of this rank then lie in the GPU's own NUMA node
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -671,7 +673,7 @@ def main():
                 roofline=dict(bound="hbm", kernel="gdn_decode_kernel<1>", achieved=dec["achieved_gbs"], peak=peaks["hbm_gbs"], unit="GB/s",
                               frac=dec["frac"], peak_source=peaks["source"], launch_us=dec["launch_us"],
                               algorithmic_bytes_per_launch=B_DECODE * DECODE_BYTES_PER_SEQ_LAYER, traffic=DECODE_TRAFFIC_NCU),
-                device_status=status)
+                device_status=status, host_binding=host_binding)
     if not args.no_extra:
         if world == 1:
             # in a child process: whatever happens there, the headline above survives

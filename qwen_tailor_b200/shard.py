@@ -75,3 +75,34 @@ def shard_varlen_batch(lengths: Sequence[int], rank: int, world: int):
     for a, b in ranges:
         cu.append(cu[-1] + (b - a))
     return mine, ranges, cu
+
+
+def bind_host_to_gpu(device_index: int) -> dict:
+    """Pin the calling process to the CPUs of the NUMA node the GPU hangs off, so that pinned host buffers allocated afterwards lie
+    in that node's memory and host<->device copies do not cross the socket interconnect.  With eight ranks each moving tens of GB/s
+    between pinned memory and its GPU, copies through the other socket's memory are what saturates first.  Changes nothing on the
+    GPU; a no-op (reported in the returned dict) where the platform does not expose the topology.  Linux only."""
+    import os
+    info = {"bound": False}
+    try:
+        p = torch.cuda.get_device_properties(device_index)
+        bdf = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        info.update(pci=bdf, numa_node=node)
+        if node < 0:
+            return info
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            spec = f.read().strip()
+        cpus = set()
+        for part in spec.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return info
+        os.sched_setaffinity(0, allowed)
+        info.update(bound=True, cpus=len(allowed))
+    except (OSError, ValueError, AttributeError, RuntimeError) as e:
+        info["error"] = type(e).__name__
+    return info
