@@ -205,3 +205,26 @@ def _gather_worker(rank, world, port, T):
 
 def test_gather_heads_world_size_2_gloo():
     mp.spawn(_gather_worker, args=(2, _free_port(), 37), nprocs=2, join=True)
+
+
+def test_bind_host_to_gpu_is_harmless_without_a_gpu():
+    """The NUMA binding used by the multi-GPU bench reports what it did and never raises, whatever the platform exposes."""
+    from qwen_tailor_b200.shard import bind_host_to_gpu
+    before = os.sched_getaffinity(0)
+    info = bind_host_to_gpu(0)
+    assert isinstance(info, dict) and "bound" in info
+    if not info["bound"]:
+        assert os.sched_getaffinity(0) == before
+
+
+def test_workspace_sizing_functions_need_no_gpu():
+    """Host arithmetic of the C ABI: the record buffer of a packed prefill batch and the prefill-attention workspace."""
+    from qwen_tailor_b200 import _lib
+    lib = _lib.load()
+    # one record of 17,152 bytes per (chunk, head); a sequence of T tokens owns T // 64 + 1 chunk slots
+    assert lib.gdn_prefill_workspace_bytes(1, 2048, 16) == (2048 // 64 + 1) * 16 * 17152
+    assert lib.gdn_prefill_workspace_bytes(3, 64 + 1 + 130, 16) == ((64 + 1 + 130) // 64 + 3) * 16 * 17152
+    assert lib.gqa_prefill_attn_workspace_bytes(1024, 0) > 0          # short prefill: the heaviest query blocks may be split
+    assert lib.gqa_prefill_attn_workspace_bytes(16384, 0) == 0        # long prefill: several blocks per SM already
+    assert lib.gqa_prefill_attn_workspace_bytes(64, 0) == 0           # a single tile per block: nothing to split
+    assert lib.gqa_decode_workspace_bytes(16, 8192) > 16 * 2 * 16 * 256 * 4

@@ -118,3 +118,33 @@ def test_accept_length():
     toks = np.array([[5, 1, 2, 3], [5, 1, 9, 3], [5, 7, 2, 3], [5, 1, 2, 8]])
     ids = np.array([[1, 2, 3, 4], [1, 2, 3, 4], [1, 2, 3, 4], [1, 2, 3, 4]])
     assert orc.accept_length(toks, ids).tolist() == [3, 1, 0, 2]
+
+
+def test_prefill_attention_oracle_equals_the_decode_oracle_row_by_row():
+    """The causal prefill oracle (qwen35/model.py:165) against the decode oracle (qwen35/batch.py:141-227) used one query at a time: query i
+    of a chunk that starts at `pos` sees the pos + i cached keys and itself."""
+    rng = np.random.default_rng(3)
+    S, pos = 9, 5
+    q = synth.bf16r(rng.standard_normal((S, 8, 256)))
+    K = synth.bf16r(rng.standard_normal((2, pos + S, 256)))
+    V = synth.bf16r(rng.standard_normal((2, pos + S, 256)))
+    full = orc.prefill_attention(q, K, V, pos)
+    for i in range(S):
+        n = pos + i
+        row = orc.attn_rows(q[i:i + 1], K[:, n][None], V[:, n][None], K[:, :n], V[:, :n])
+        assert np.allclose(full[i], row[0], rtol=1e-12, atol=1e-12)
+
+
+def test_gated_norm_oracle_properties():
+    """silu(z) * w * y / rms(y) (qwen35/prefill.py:137-157): scaling y leaves the result unchanged up to the epsilon, a zero gate
+    input gives zero, and the result is bf16-valued."""
+    rng = np.random.default_rng(4)
+    y = synth.bf16r(rng.standard_normal((3, 2048)))
+    proj = synth.bf16r(rng.standard_normal((3, 8224)))
+    gw = (1.0 + 0.1 * rng.standard_normal(128)).astype(np.float32)
+    out = orc.gated_norm(y, proj, gw)
+    assert out.shape == (3, 2048) and np.array_equal(out, synth.bf16r(out))
+    out2 = orc.gated_norm(synth.bf16r(4.0 * y), proj, gw)            # a power of two: exact in bf16
+    assert np.max(np.abs(out2.astype(np.float64) - out)) <= 2.0 ** -7 * np.max(np.abs(out))
+    proj0 = proj.copy(); proj0[:, 6144:8192] = 0
+    assert not np.any(orc.gated_norm(y, proj0, gw))
