@@ -236,6 +236,12 @@ GDN_API int gdn_gated_norm(const void* y, const void* proj, long long row_stride
 GDN_API int gdn_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,
                    long long sstride, void* stream);
 
+/* hist[slots[b], pos[b], :] = rows[b, :] for b < B: the hidden-state history of the speculative mode, written in place.
+ * Replaces: hrec, qwen35/batch.py:375-399.
+ *   hist bf16 [n_slots, Lh, H];  rows bf16 [B, H];  slots, pos int32 [B] on the device (an out-of-range entry skips its row and sets
+ *   device status 1). */
+GDN_API int gdn_hrec(void* hist, const void* rows, const int* slots, const int* pos, int B, int n_slots, int Lh, int H, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

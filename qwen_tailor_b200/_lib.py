@@ -47,6 +47,7 @@ SIGNATURES = {
     "gdn_conv_prep": (I, [P, LL, P, P, P, P, P, P, I, P]),
     "gdn_gated_norm": (I, [P, P, LL, P, P, LL, P]),
     "gdn_state_copy": (I, [P, P, I, LL, LL, LL, I, LL, LL, P]),
+    "gdn_hrec": (I, [P, P, P, P, I, I, I, I, P]),
 }
 
 

@@ -110,8 +110,15 @@ def blit(dst, src, n, d0, s0, ny=1, dstride=0, sstride=0):
 
 def hrec(hist, Hn, slots, pos):
     """hist[slots[b], pos[b], :] = Hn[b]  (in place; hist [S+1, Lh, H] bf16): the hidden-state history of speculative mode
-    (batch.py:393-399).  Row scatter through torch indexing: it moves B rows of 2 KiB and is not a measured kernel."""
-    hist[slots.long(), pos.long()] = Hn
+    (batch.py:375-399).  slots, pos: int32 [B] on the device; an out-of-range entry skips its row and sets the device status.
+    Returns hist (the reference returns a token to evaluate; here stream order does that job)."""
+    _lib.require_cuda(hist, Hn, slots, pos)
+    assert hist.dtype == torch.bfloat16 and Hn.dtype == torch.bfloat16 and hist.is_contiguous() and hist.dim() == 3
+    assert slots.dtype == torch.int32 and pos.dtype == torch.int32
+    Hn = Hn.contiguous()
+    B, H = Hn.shape
+    assert hist.shape[2] == H and slots.numel() == B and pos.numel() == B
+    check(_lib.load().gdn_hrec(ptr(hist), ptr(Hn), ptr(slots), ptr(pos), B, hist.shape[0], hist.shape[1], H, stream_ptr(hist.device)), "hrec")
     return hist
 
 

@@ -338,4 +338,12 @@ int gdn_state_copy(void* dst, const void* src, int elem_size, long long n, long 
     return launch_state_copy(dst, src, elem_size, n, d0, s0, ny, dstride, sstride, static_cast<cudaStream_t>(stream));
 }
 
+int gdn_hrec(void* hist, const void* rows, const int* slots, const int* pos, int B, int n_slots, int Lh, int H, void* stream) {
+    REQUIRE(hist && rows && slots && pos, GDN_E_NULL, "gdn_hrec: null pointer");
+    REQUIRE(B >= 0 && n_slots > 0 && Lh > 0 && H > 0, GDN_E_SHAPE, "gdn_hrec: B=%d n_slots=%d Lh=%d H=%d", B, n_slots, Lh, H);
+    int* status = status_ptr();
+    REQUIRE(status, GDN_E_LAUNCH, "gdn_hrec: no CUDA device");
+    return launch_hrec(hist, rows, slots, pos, B, n_slots, Lh, H, status, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

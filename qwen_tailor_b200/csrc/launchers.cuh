@@ -117,6 +117,7 @@ int launch_gqa_prefill(const void* q, const void* k, const void* v, void* out, i
 size_t gqa_prefill_workspace_bytes(int S, int pos);
 
 // ---- state_copy.cu ----
+int launch_hrec(void* hist, const void* rows, const int* slots, const int* pos, int B, int n_slots, int Lh, int H, int* status, cudaStream_t st);
 int launch_state_copy(void* dst, const void* src, int elem_size, long long n, long long d0, long long s0, int ny, long long dstride,
                       long long sstride, cudaStream_t st);
 

@@ -37,4 +37,30 @@ int launch_state_copy(void* dst, const void* src, int elem_size, long long n, lo
     return run<uint16_t>(dst, src, n, d0, s0, ny, dstride, sstride, st);
 }
 
+// Row scatter of the speculative mode's hidden-state history (the reference's `hrec` kernel, qwen35/batch.py:375-399):
+//     hist[slots[b], pos[b], :] = rows[b, :]        hist [n_slots, Lh, H] bf16, rows [B, H] bf16
+// The indices live on the device; a row whose slot or position is out of range is skipped and reported through the status word.
+__global__ void hrec_kernel(__nv_bfloat16* __restrict__ hist, const __nv_bfloat16* __restrict__ rows, const int* __restrict__ slots,
+                            const int* __restrict__ pos, int n_slots, int Lh, int H, int* status) {
+    const int b = blockIdx.y;
+    const int s = slots[b], p = pos[b];
+    if (s < 0 || s >= n_slots || p < 0 || p >= Lh) { if (threadIdx.x == 0 && blockIdx.x == 0) atomicExch(status, 1); return; }
+    __nv_bfloat16* d = hist + ((size_t)s * Lh + p) * H;
+    const __nv_bfloat16* r = rows + (size_t)b * H;
+    const bool vec = (H % 8 == 0) && (reinterpret_cast<uintptr_t>(d) % 16 == 0) && (reinterpret_cast<uintptr_t>(r) % 16 == 0);
+    if (vec) {
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H / 8; i += gridDim.x * blockDim.x)
+            reinterpret_cast<uint4*>(d)[i] = reinterpret_cast<const uint4*>(r)[i];
+    } else {
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) d[i] = r[i];
+    }
+}
+
+int launch_hrec(void* hist, const void* rows, const int* slots, const int* pos, int B, int n_slots, int Lh, int H, int* status, cudaStream_t st) {
+    if (B <= 0 || H <= 0) return GDN_OK;
+    if (B > 65535) { set_error("hrec: B = %d exceeds 65535", B); return GDN_E_SHAPE; }
+    hrec_kernel<<<dim3(1, B), 128, 0, st>>>(static_cast<__nv_bfloat16*>(hist), static_cast<const __nv_bfloat16*>(rows), slots, pos, n_slots, Lh, H, status);
+    return check_launch("hrec");
+}
+
 }  // namespace gdn

@@ -170,6 +170,12 @@ def test_hrec_scatters_rows(dev):
         assert torch.equal(hist[s, p], Hn[b])
     assert int((hist != 0).any(-1).sum()) == 3, "only the three addressed rows change"
     assert _lib.device_status() == 0
+    # an odd width takes the element-wise path; a bad slot or position skips its row and is reported
+    hist2 = torch.zeros((4, 16, 1001), dtype=torch.bfloat16, device=dev)
+    Hn2 = torch.randn((3, 1001), device=dev).to(torch.bfloat16)
+    hrec(hist2, Hn2, i32_dev([1, 9, 2], dev), i32_dev([3, 0, 16], dev))
+    assert torch.equal(hist2[1, 3], Hn2[0]) and int((hist2 != 0).any(-1).sum()) == 1
+    assert _lib.device_status() == 1 and _lib.device_status() == 0
 
 
 def test_attn_paged_static_wrapper_equals_attn_paged(dev):
