@@ -100,7 +100,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     __shared__ uint64_t bars[B_COUNT];
     __shared__ uint32_t tmem_slot;
     __shared__ int s_abort;
-    __shared__ int s_group_ok[2];                                    // verdict of the chain / output group's polling warp on its last wait
+    __shared__ int s_group_ok[2];                                    // outcome reported by the chain / output group's polling warp on its last wait
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = blockIdx.x / a.n_heads, h = a.head_lo + blockIdx.x % a.n_heads;
@@ -167,7 +167,7 @@ gdn_phase_b_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // Waits of a warp group.  One warp polls the mbarrier and the others block on a hardware barrier: a polling warp takes issue
     // slots on its scheduler, and the scheduler of the MMA-issuing warp must stay free of pollers (measured: with all fourteen
     // warps polling, every wait of the issuing thread cost ~300 cycles even when its barrier had long completed).  The polling
-    // warp's verdict is published before the group barrier, so the whole group takes the same exit -- a warp that left on its
+    // warp's outcome is published before the group barrier, so the whole group takes the same exit -- a warp that left on its
     // own would strand the others at a barrier that has no timeout.
     auto chain_wait = [&](int b, uint32_t parity) -> bool {        // warps 0-7; warp 1 polls (warp 12 issues MMAs on scheduler 0)
         if (warp == 1) { const bool okw = wait(b, parity); if (lane == 0) s_group_ok[0] = okw ? 1 : 0; }
