@@ -154,11 +154,14 @@ class PrefixCache:
     def __init__(self, budget_mb=1024, enabled=True, page_size=64, kv_pages=None, kv_share=0.5):
         """budget_mb: bytes the cache may hold (recurrent states + the pages its checkpoints added).  The page pool is created at
         the first insert (it needs the layer count and the device); its capacity is ``kv_pages`` pages, or ``kv_share`` of the
-        budget.  A server that runs its live sequences on the same pool (restore_paged) sizes it with ``kv_pages``."""
+        budget.  A server that runs its live sequences on the same pool (restore_paged) sizes it with ``kv_pages``, or passes its
+        own ``PagePool`` (``PagedPools.pages``) as ``kv_pages``."""
         self.budget = int(budget_mb * (1 << 20))
         self.enabled = enabled
         self.page_size, self._kv_pages, self._kv_share = page_size, kv_pages, kv_share
         self.pool: Optional[PagePool] = None
+        if isinstance(kv_pages, PagePool):                          # the server's own pool (PagedPools.pages): live sequences and
+            self.pool, self.page_size, self._kv_pages = kv_pages, kv_pages.page_size, kv_pages.n_pages      # checkpoints share pages
         self.nodes: Dict[int, Node] = {}
         self.bytes = 0
         self._clock = 0

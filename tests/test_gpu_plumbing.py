@@ -236,3 +236,72 @@ def test_verify_64_sequences_4_tokens_equal_solo_rows(dev):
         assert torch.equal(y[b * M:(b + 1) * M], yb) and torch.equal(ssm[e], sb) and torch.equal(conv[e * 2 + (p ^ 1)], cb)
         assert torch.equal(conv[e * 2 + p], conv0[e * 2 + p]), "the buffer that was read is preserved"
     assert torch.equal(ssm[B], ssm0[B]) and _lib.device_status() == 0
+
+
+def test_paged_pools_serve_decode_steps_and_share_pages_with_the_prefix_cache(dev):
+    """PagedPools (K/V of the slots in the prefix cache's page pool) against the reference-layout Pools: the same attention and
+    delta-rule outputs over several decode steps; a checkpoint taken from a slot shares the slot's full pages, a hit hands another
+    slot those pages without copying K/V, and the two sequences then diverge on private pages."""
+    from qwen_tailor_b200.batch import attn_b
+    from qwen_tailor_b200.paged_pools import PagedPools
+    cfg = Cfg()
+    Lmax, lens = 256, [150, 70]
+    dense = Pools(cfg, 3, Lmax, device=dev)
+    paged = PagedPools(cfg, 3, Lmax, n_pages=24, device=dev)
+    g = torch.Generator(device=dev); g.manual_seed(5)
+    rnb = lambda *s: torch.randn(s, generator=g, device=dev).to(torch.bfloat16)
+    for slot, pos in enumerate(lens):
+        st = {"kv": [], "conv": [rnb(1, 3, 6144) for _ in range(cfg.n_linear)],
+              "ssm": [torch.randn((1, 16, 128, 128), generator=g, device=dev) * 0.02 for _ in range(cfg.n_linear)]}
+        for _ in range(cfg.n_full):
+            K, V = torch.zeros((1, 2, Lmax, 256), dtype=torch.bfloat16, device=dev), torch.zeros((1, 2, Lmax, 256), dtype=torch.bfloat16, device=dev)
+            K[:, :, :pos], V[:, :, :pos] = rnb(1, 2, pos, 256), rnb(1, 2, pos, 256)
+            st["kv"].append((K, V))
+        dense.load(slot, st, pos)
+        paged.admit(slot, st, pos)
+    slots = i32_dev([0, 1], dev)
+    c = synth.config2(B=2, seed=3, M=1)
+    cw, A_log, dtb = bf16_dev(c["conv_w"], dev), f32_dev(c["A_log"], dev), f32_dev(c["dt_bias"], dev)
+    cur = list(lens)
+    for step in range(3):
+        ctx = i32_dev(cur, dev)
+        for s_ in range(2):
+            paged.reserve(s_, cur[s_] + 1)
+        q, kn, vn = rnb(2, 8, 256), rnb(2, 2, 256), rnb(2, 2, 256)
+        o_d = attn_b(q, kn, vn, dense.K[1], dense.V[1], slots, ctx, M=1)
+        o_p = paged.attn(1, q, kn, vn, slots, ctx, M=1)
+        assert torch.equal(o_d, o_p)
+        proj = rnb(2, 8224)
+        y_d = deltanet_b(proj, dense.conv[2], cw, A_log, dtb, dense.ssm[2], slots, ctx)
+        y_p = paged.deltanet(2, proj, cw, A_log, dtb, slots, ctx)
+        assert torch.equal(y_d, y_p)
+        for s_ in range(2):
+            cur[s_] += 1
+            paged.advance(s_, 1)
+    # ---- a checkpoint of slot 0 (153 tokens = 2 full pages + 25 rows) shares its full pages; a hit gives them to slot 2 ----
+    pc = PrefixCache(budget_mb=256, kv_pages=paged.pages)
+    toks = np.arange(500, 500 + cur[0], dtype=np.int32)
+    node = pc.insert(None, toks, cur[0], paged.checkpoint_state(0))
+    assert node.pages[:2] == paged.owned[0][:2] and all(paged.pages.refs[p] == 2 for p in node.pages[:2])
+    hit, _ = pc.lookup(np.concatenate([toks, [7, 8]]))
+    assert hit is node
+    live, _ = pc.restore_paged(hit)
+    paged.admit_paged(2, live, cur[0])
+    assert paged.owned[2][:2] == paged.owned[0][:2] and paged.owned[2][2] != paged.owned[0][2]
+    both = i32_dev([0, 2], dev)
+    ctx = i32_dev([cur[0], cur[0]], dev)
+    paged.reserve(0, cur[0] + 1); paged.reserve(2, cur[0] + 1)
+    q1, kn1, vn1 = rnb(1, 8, 256), rnb(2, 2, 256), rnb(1, 2, 256)
+    q2 = torch.cat([q1, q1])
+    o = paged.attn(0, q2, kn1, torch.cat([vn1, vn1]), both, ctx, M=1)
+    # same cached keys, same query; the appended key differs, so the outputs differ only through the new row -- and each slot wrote
+    # its own page: the checkpoint's copy and the other slot's page are untouched
+    row = cur[0] % 64
+    assert torch.equal(paged.pages.K[0][paged.owned[0][2], :, row], kn1[0]) and torch.equal(paged.pages.K[0][paged.owned[2][2], :, row], kn1[1])
+    assert not torch.equal(o[0], o[1])
+    o_again = paged.attn(0, q2, torch.cat([kn1[:1], kn1[:1]]), torch.cat([vn1, vn1]), both, ctx, M=1)
+    assert torch.equal(o_again[0], o_again[1]) and torch.equal(o_again[0], o[0])
+    paged.release(0); paged.release(2); paged.release(1)
+    pc.clear()
+    assert paged.pages.available() == paged.pages.n_pages - 1
+    assert _lib.device_status() == 0
