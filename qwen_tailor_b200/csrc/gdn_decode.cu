@@ -227,10 +227,9 @@ __global__ void __launch_bounds__(128, Tune<MT>::BLOCKS) gdn_decode_kernel(const
                     sv[j * DV + tid] = c[2];
                     const float qs_w = warp_sum(c[0] * c[0]), ks_w = warp_sum(c[1] * c[1]);
                     if (lane == 0) { sred[(2 * j) * 4 + warp] = qs_w; sred[(2 * j + 1) * 4 + warp] = ks_w; }
-                    if (tid == 32 * (j & 3)) {                   // the tokens' gates on different warps: side by side, not one after the other
-                        sgate[2 * j] = expf(log_decay(expA, rawf(in.a[j]), dtb));
-                        sgate[2 * j + 1] = sigmoid_bf16(rawf(in.b[j]));
-                    }
+                    // the gates of the chained tokens on different warps (decay on one, beta on another): side by side, not in a row
+                    if (tid == 32 * (j & 3)) sgate[2 * j] = expf(log_decay(expA, rawf(in.a[j]), dtb));
+                    if (tid == 32 * ((j + 2) & 3)) sgate[2 * j + 1] = sigmoid_bf16(rawf(in.b[j]));
                     // conv-window snapshot j = input rows j-2, j-1, j (kernels.py:528-541); written by the block that owns slice 0
                     if (sl == 0 && sp.ok) {
 #pragma unroll
