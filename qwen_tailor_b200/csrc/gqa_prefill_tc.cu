@@ -325,7 +325,13 @@ gqa_prefill_tc_kernel(const PrefillAttnArgs a, const __grid_constant__ CUtensorM
         const float* other = nullptr;
         bool write_out = true;
         if (nparts == 2) {
-            float* mine = reinterpret_cast<float*>(a.ws + ws_parts_off16) + ((size_t)unit * 2 + part) * PF_PART_FLOATS + (size_t)row * (ATT_D + 4);
+            // The partial travels as one bulk copy each way: the rings are idle now (every tile has been consumed), so the rows are
+            // staged there -- a thread's row is 1 KiB, written row by row the global stores would be 32 scattered segments per
+            // instruction -- and the half that arrives last fetches the other half's image the same way.
+            float* stage_f = reinterpret_cast<float*>(smem + PF_Q_BYTES);
+            float* mine_s = stage_f + (size_t)row * (ATT_D + 4);
+            float* mine_g = reinterpret_cast<float*>(a.ws + ws_parts_off16) + ((size_t)unit * 2 + part) * PF_PART_FLOATS;
+            const float* other_g = reinterpret_cast<const float*>(a.ws + ws_parts_off16) + ((size_t)unit * 2 + (part ^ 1)) * PF_PART_FLOATS;
 #pragma unroll 1
             for (int c0 = 0; c0 < 256; c0 += 32) {
                 uint32_t o[32];
@@ -333,18 +339,32 @@ gqa_prefill_tc_kernel(const PrefillAttnArgs a, const __grid_constant__ CUtensorM
                 tmem_wait_ld();
 #pragma unroll
                 for (int i = 0; i < 32; i += 4)
-                    *reinterpret_cast<float4*>(mine + c0 + i) = make_float4(__uint_as_float(o[i]), __uint_as_float(o[i + 1]), __uint_as_float(o[i + 2]), __uint_as_float(o[i + 3]));
+                    *reinterpret_cast<float4*>(mine_s + c0 + i) = make_float4(__uint_as_float(o[i]), __uint_as_float(o[i + 1]), __uint_as_float(o[i + 2]), __uint_as_float(o[i + 3]));
             }
-            *reinterpret_cast<float2*>(mine + ATT_D) = make_float2(m_run, l_run);
-            __threadfence();
+            *reinterpret_cast<float2*>(mine_s + ATT_D) = make_float2(m_run, l_run);
+            fence_proxy_async_smem();
             asm volatile("bar.sync 1, 128;" ::: "memory");           // the four softmax warps
-            if (tid == 0) s_last = (!aborted() && arrive(1 + unit) == 1u) ? 1 : 0;
+            if (tid == 0) {
+                asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                             ::"l"(mine_g), "r"(smem_addr(stage_f)), "r"((uint32_t)(PF_PART_FLOATS * 4)) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // the image is written (not merely read out of shared memory)
+                __threadfence();
+                s_last = (!aborted() && arrive(1 + unit) == 1u) ? 1 : 0;
+                if (s_last) {
+                    __threadfence();
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                    mbar_expect_tx(bar(PB_QFULL), (uint32_t)(PF_PART_FLOATS * 4));      // (second use of this barrier: phase 1)
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(smem_addr(stage_f)), "l"(other_g), "r"((uint32_t)(PF_PART_FLOATS * 4)), "r"(bar(PB_QFULL)) : "memory");
+                }
+            }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             write_out = s_last != 0;
             if (write_out) {
-                __threadfence();
-                other = reinterpret_cast<const float*>(a.ws + ws_parts_off16) + ((size_t)unit * 2 + (part ^ 1)) * PF_PART_FLOATS + (size_t)row * (ATT_D + 4);
-                const float2 ml = __ldcg(reinterpret_cast<const float2*>(other + ATT_D));
+                if (!wait(PB_QFULL, 1)) write_out = false;
+                other = mine_s;                                      // the other half's row now sits where this thread's did
+                const float2 ml = *reinterpret_cast<const float2*>(other + ATT_D);
                 const float m = fmaxf(m_run, ml.x);
                 w_own = m_run == -INFINITY ? 0.f : exp2f(m_run - m);
                 w_other = ml.x == -INFINITY ? 0.f : exp2f(ml.x - m);
@@ -363,7 +383,7 @@ gqa_prefill_tc_kernel(const PrefillAttnArgs a, const __grid_constant__ CUtensorM
                 if (other) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) {
-                        const float4 x = __ldcg(reinterpret_cast<const float4*>(other + c0 + i));
+                        const float4 x = *reinterpret_cast<const float4*>(other + c0 + i);
                         const float xs[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
@@ -425,8 +445,9 @@ static bool make_map3(CUtensorMap* m, const void* base, long long n1, long long 
 static int pf_heavy_threshold(int S, int pos) {
     const int n_qb = (S + PF_QTOK - 1) / PF_QTOK;
     const int t_max = pf_tiles_of(n_qb - 1, S, pos);
-    // splitting pays while there are too few blocks to balance the causal triangle over the SMs, and only for long key ranges
-    if (2 * n_qb > 2 * 148 || t_max < 4) return 0;
+    // splitting pays while there is at most one block per SM (the launch then lasts as long as the last query block), and only for
+    // key ranges long enough to outweigh the merge (measured: S = 1024 and 2048 gain 12-13%, S = 512 and S = 4096 lose)
+    if (2 * n_qb > 148 || t_max < 6) return 0;
     return max(2, (t_max + 1) / 2);
 }
 size_t gqa_prefill_workspace_bytes(int S, int pos) {

@@ -225,6 +225,6 @@ def test_workspace_sizing_functions_need_no_gpu():
     assert lib.gdn_prefill_workspace_bytes(1, 2048, 16) == (2048 // 64 + 1) * 16 * 17152
     assert lib.gdn_prefill_workspace_bytes(3, 64 + 1 + 130, 16) == ((64 + 1 + 130) // 64 + 3) * 16 * 17152
     assert lib.gqa_prefill_attn_workspace_bytes(1024, 0) > 0          # short prefill: the heaviest query blocks may be split
-    assert lib.gqa_prefill_attn_workspace_bytes(16384, 0) == 0        # long prefill: several blocks per SM already
+    assert lib.gqa_prefill_attn_workspace_bytes(4096, 0) == 0         # long prefill: more than one block per SM already
     assert lib.gqa_prefill_attn_workspace_bytes(64, 0) == 0           # a single tile per block: nothing to split
     assert lib.gqa_decode_workspace_bytes(16, 8192) > 16 * 2 * 16 * 256 * 4
