@@ -44,10 +44,10 @@ STATE_BYTES = HV * DV * DK * 4
 # algorithmic bytes of one decode step of one (sequence, layer): state read + state written + mixed-qkv row + conv window read
 # + conv window written + y  (M = 1)
 DECODE_BYTES_PER_SEQ_LAYER = 2 * STATE_BYTES + CD * 2 + 3 * CD * 2 + 3 * CD * 2 + HV * DV * 2
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at B=64 from an ncu capture of this kernel (70.34 MB read +
-# 12.64 MB written; the rest of the 67 MB of state written by a launch is still in L2 when the kernel ends and is written back
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch at B=64 from an ncu capture of this kernel (70.35 MB read +
+# 11.57 MB written; the rest of the 67 MB of state written by a launch is still in L2 when the kernel ends and is written back
 # during the following launches)
-DECODE_TRAFFIC_NCU = 82978816
+DECODE_TRAFFIC_NCU = 81920000
 PREFILL_FLOP_PER_TOKEN_LAYER = HV * (8 * 64 * 128 + 6 * 128 * 128)        # chunk 64: 2,621,440
 PREFILL_BYTES_PER_TOKEN_LAYER = 4 * HV * 128 * 2 + 2 * HV * 4                # q,k,v,y bf16 + log-decay, beta fp32 = 16,512
 # values of the device status word (a kernel that meets one of these skips the row or leaves; nothing faults)
