@@ -136,6 +136,10 @@ gqa_decode_tc_kernel(const AttnArgs a, const __grid_constant__ CUtensorMap tmK, 
     const int M = a.M, P = a.P;
     const uint32_t sbase = smem_addr(smem);
     if (sbase & 1023u) { if (tid == 0) atomicExch(a.status, 4); return; }
+    // Programmatic dependent launch: the next kernel of the stream may be scheduled onto SMs as this one leaves them, and this one
+    // waits here -- before it reads anything an earlier kernel may have written -- until its predecessors have completed.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- the plan, computed by every block for itself (a few hundred integer operations; a kernel of its own in front of this one
     //      costs a launch and a dependent start per layer).  Same plan as gqa_decode_plan_kernel: the tiles of all pairs laid end to
@@ -651,7 +655,13 @@ int launch_gqa_decode_tc(const AttnArgs& a, const CUtensorMap& tk, const CUtenso
             return check_launch("gqa_decode_tc smem attribute");
         attr_set[dev] = true;
     }
-    gqa_decode_tc_kernel<<<a.G, TC_THREADS, TC_SMEM, stream>>>(a, tk, tv);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)a.G); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = TC_SMEM; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, gqa_decode_tc_kernel, a, tk, tv);
     return check_launch("gqa_decode_tc");
 }
 
